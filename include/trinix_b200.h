@@ -1,0 +1,173 @@
+/*
+ * trinix_b200 — C ABI of the sm_100a (B200) backend for Trinix's layer forward path.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers, sizes and
+ * strides (in ELEMENTS unless a name ends in `_bytes`), enqueues work on the
+ * given CUDA stream and returns a status code (0 = ok, < 0 = error). Nothing
+ * here allocates device memory, synchronises the stream or throws. Arguments
+ * are validated before any launch; an error code means nothing was launched.
+ * The caller owns every buffer and selects the device (cudaSetDevice) first.
+ *
+ * Each declaration names the interface of the reference (Trinix 0.1.4, paths
+ * relative to its repository root) whose device work it replaces.
+ */
+#ifndef TRINIX_B200_H_
+#define TRINIX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TRX_ABI_VERSION 1
+
+typedef enum trx_status {
+  TRX_OK = 0,
+  TRX_ERR_NULL_POINTER = -1,  /* a required pointer is NULL */
+  TRX_ERR_DTYPE = -2,         /* dtype code not supported by this entry point */
+  TRX_ERR_SHAPE = -3,         /* negative / zero / inconsistent sizes */
+  TRX_ERR_ALIGNMENT = -4,     /* pointer or stride not aligned as required */
+  TRX_ERR_STRIDE = -5,        /* stride smaller than the extent it spans */
+  TRX_ERR_UNSUPPORTED = -6,   /* legal request this build cannot serve (e.g. head_dim) */
+  TRX_ERR_CUDA = -7,          /* the CUDA runtime/driver reported an error at launch */
+  TRX_ERR_DEVICE_STATUS = -8, /* a kernel recorded a bounded-wait timeout in its status word */
+  TRX_ERR_WORKSPACE = -9      /* workspace missing or too small */
+} trx_status;
+
+typedef enum trx_dtype { TRX_F32 = 0, TRX_F16 = 1, TRX_BF16 = 2 } trx_dtype;
+
+typedef enum trx_glu_act {
+  TRX_GLU_SWIGLU = 0,     /* up * silu(gate) */
+  TRX_GLU_GEGLU_TANH = 1, /* up * gelu_tanh(gate) */
+  TRX_GLU_REGLU = 2       /* up * max(gate, 0) */
+} trx_glu_act;
+
+/* ABI version of the loaded library (TRX_ABI_VERSION at build time). */
+int trx_version(void);
+
+/* Static, human-readable text for a status code. */
+const char* trx_status_string(int code);
+
+/*
+ * RMSNorm forward over R rows of C columns:
+ *   rstd = 1/sqrt(mean(x^2) + eps);  y = round_x(w * round_x(x * rstd))
+ * (the two roundings to the activation dtype follow the reference's PyTorch
+ * backend, trinix/layers/norm/rmsnorm.py:70-75). `rstd_or_null` receives the
+ * fp32 per-row rstd when non-NULL.
+ * Replaces the launch made by TritonRMSNormFunction.forward,
+ * trinix/kernels/rmsnorm_kernel.py:238-269 (kernel :9-61), reached through
+ * TritonRMSNormKernel.apply, trinix/kernels/rmsnorm_kernel.py:387-389.
+ */
+int trx_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd_or_null, int64_t R,
+                    int64_t C, int64_t x_row_stride, int64_t y_row_stride, float eps, int x_dtype,
+                    int w_dtype, void* stream);
+
+/*
+ * LayerNorm forward: y = (x - mean) * rstd * w + b with biased variance.
+ * `w_or_null` / `b_or_null` may be NULL (elementwise_affine=False,
+ * trinix/layers/norm/layernorm.py:54-55); both share `wb_dtype`.
+ * Replaces TritonLayerNormFunction.forward, trinix/kernels/layernorm_kernel.py:224-353
+ * (kernel :11-67), reached through TritonLayerNormKernel.apply, :418-422.
+ */
+int trx_layernorm_fwd(const void* x, const void* w_or_null, const void* b_or_null, void* y,
+                      float* mean_or_null, float* rstd_or_null, int64_t R, int64_t C,
+                      int64_t x_row_stride, int64_t y_row_stride, float eps, int x_dtype,
+                      int wb_dtype, void* stream);
+
+/*
+ * Per-row symmetric int8 quantisation:
+ *   scale[r] = max|x[r,:]| / 127 (fp32, IEEE division)
+ *   code     = clamp(round_half_even(x / scale), -127, 127); zero rows -> scale 0, codes 0.
+ * No counterpart in the reference (it has no int8 code); the contract is the
+ * "per-row symmetric int8 quantize/dequantize" configuration of this project's baseline.
+ */
+int trx_quant_rowwise_i8(const void* x, int8_t* codes, float* scales, int64_t R, int64_t C,
+                         int64_t x_row_stride, int64_t codes_row_stride, int x_dtype,
+                         void* stream);
+
+/*
+ * Inverse of trx_quant_rowwise_i8: y = round_y(float(code) * scale[r]).
+ * No counterpart in the reference.
+ */
+int trx_dequant_rowwise_i8(const int8_t* codes, const float* scales, void* y, int64_t R, int64_t C,
+                           int64_t codes_row_stride, int64_t y_row_stride, int y_dtype,
+                           void* stream);
+
+/*
+ * Fused RMSNorm -> int8: quantises exactly the rows trx_rmsnorm_fwd would
+ * write (after rounding to the activation dtype) without writing them.
+ * No counterpart in the reference; its structure (norm, then an epilogue on
+ * the row held on chip) is that of fused_rmsnorm_activation_forward_kernel,
+ * trinix/kernels/fused/rmsnorm_activation_kernel.py:9-77.
+ */
+int trx_rmsnorm_quant_i8(const void* x, const void* w, int8_t* codes, float* scales, int64_t R,
+                         int64_t C, int64_t x_row_stride, int64_t codes_row_stride, float eps,
+                         int x_dtype, int w_dtype, void* stream);
+
+/*
+ * Rotary position embedding, half-split ("rotate_half") form, q and k in one launch:
+ *   o[..., :D/2] = x1*cos - x2*sin ;  o[..., D/2:] = x2*cos + x1*sin
+ * with cos/sin rows indexed by the sequence position (tables are (S, >= D/2),
+ * only the first D/2 columns are read). Tensors are (B, S, H, D) with D
+ * contiguous; q and k may have different head counts and arbitrary b/s/h strides.
+ * `table_dtype` is TRX_F32 or equal to `x_dtype`; in the latter case every
+ * intermediate product is rounded to `x_dtype` like the reference's PyTorch path
+ * (trinix/layers/embeddings/rope.py:111-118). `inverse != 0` negates sin.
+ * Replaces TritonRoPEFunction.forward, trinix/kernels/rope_kernel.py:165-170
+ * (two launches of _rope_rotation_kernel, :11-88), reached through
+ * TritonRoPEKernel.apply, :209-213.
+ */
+int trx_rope_fwd(const void* q, const void* k, const void* cos_table, const void* sin_table,
+                 void* q_out, void* k_out, int64_t B, int64_t S, int64_t Hq, int64_t Hk, int64_t D,
+                 const int64_t q_strides[3], const int64_t k_strides[3],
+                 const int64_t qo_strides[3], const int64_t ko_strides[3],
+                 int64_t table_row_stride, int table_dtype, int x_dtype, int inverse,
+                 void* stream);
+
+/*
+ * Gated linear unit forward: y[r, c] = up[r, c] * act(gate[r, c]) for R rows of H columns.
+ * `up` and `gate` are separate pointers with their own row strides so that both the
+ * reference's concatenated layout (x[..., :H] = up, x[..., H:] = gate) and
+ * separate tensors work.
+ * Replaces TritonSwiGLUFunction.forward (trinix/kernels/swigelu_kernel.py:121-152),
+ * the GeGLU forward (trinix/kernels/geglu_kernel.py:9-49) and the ReGLU forward
+ * (trinix/kernels/reglu_kernel.py:9-41), reached through Triton{SwiGLU,GeGLU,ReGLU}Kernel.apply.
+ */
+int trx_glu_fwd(const void* up, const void* gate, void* y, int64_t R, int64_t H,
+                int64_t up_row_stride, int64_t gate_row_stride, int64_t y_row_stride, int act,
+                int dtype, void* stream);
+
+/* Bytes of zero-initialised device workspace trx_attn_fwd needs (status word + scheduler state). */
+size_t trx_attn_workspace_bytes(void);
+
+/*
+ * Attention forward, softmax(scale * Q K^T + bias) V with online softmax:
+ *   q (B, Sq, Hq, D), k/v (B, Sk, Hk, D), out (B, Sq, Hq, D); D contiguous, D in {64, 128};
+ *   Hq % Hk == 0, query head h reads kv head h / (Hq / Hk)  (GQA / MQA natively; a kv head
+ *   stride of 0 — an expanded single head — is accepted);
+ *   causal: key j visible to query i iff j <= i;
+ *   window_left/right >= 0: visible iff -left <= j - i <= right (pass -1/-1 for no window);
+ *   slopes_or_null: fp32 [Hq], adds -slope[h] * |i - j| after scaling (ALiBi);
+ *   lse_or_null: fp32 (B, Hq, Sq) natural-log sum-exp per row, optional.
+ * `workspace` points at trx_attn_workspace_bytes() bytes that were zero when first used;
+ * word 0 accumulates a non-zero code if a bounded on-chip wait ever gave up.
+ * strides are (batch, seq, head) in elements. dtype: TRX_BF16 or TRX_F16.
+ * Replaces TritonAttentionKernel.apply, trinix/kernels/attention_kernel.py:498-664
+ * (kernel _fwd_kernel, :235-434), reached through triton_attn_func,
+ * trinix/layers/attention/functional.py:8-140, and the flash_attn_func call at
+ * trinix/layers/attention/base.py:338-344.
+ */
+int trx_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse_or_null,
+                 const float* slopes_or_null, int64_t B, int64_t Sq, int64_t Sk, int64_t Hq,
+                 int64_t Hk, int64_t D, const int64_t q_strides[3], const int64_t k_strides[3],
+                 const int64_t v_strides[3], const int64_t o_strides[3], float scale, int causal,
+                 int64_t window_left, int64_t window_right, int dtype, void* workspace,
+                 size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TRINIX_B200_H_ */

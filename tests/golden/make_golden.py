@@ -1,0 +1,126 @@
+"""Generate the golden vectors under tests/golden/ by running the REFERENCE itself.
+
+    PYTHONPATH=/path/to/trinix-reference python tests/golden/make_golden.py
+
+Imports the unmodified reference package (Trinix 0.1.4), runs its PyTorch backend on CPU
+(no CUDA here, so every module takes `_pytorch_forward`) on small seeded inputs and stores
+inputs and outputs in `reference_vectors.npz`. bf16 tensors are stored as their uint16 bit
+patterns (key suffix `_bf16`). The reference has no int8 code, so there are no int8 vectors.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+REF = os.environ.get("TRINIX_REFERENCE", "/root/reference")
+sys.path.insert(0, REF)
+
+import trinix  # noqa: E402
+from trinix.layers.activation.geglu import FastGeGLU  # noqa: E402
+from trinix.layers.activation.reglu import FastReGLU  # noqa: E402
+from trinix.layers.activation.swigelu import FastSwiGLU  # noqa: E402
+from trinix.layers.attention.base import FastBaseAttention  # noqa: E402
+from trinix.layers.attention.grouped_query_attention import FastGroupedQueryAttention  # noqa: E402
+from trinix.layers.embeddings.alibi import FastALiBiPositionEmbedding  # noqa: E402
+from trinix.layers.embeddings.rope import FastRoPEPositionEmbedding  # noqa: E402
+from trinix.layers.norm.layernorm import FastLayerNorm  # noqa: E402
+from trinix.layers.norm.rmsnorm import FastRMSNorm  # noqa: E402
+
+OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz")
+vec = {}
+
+
+def put(name, t):
+    t = t.detach()
+    if t.dtype == torch.bfloat16:
+        vec[name + "_bf16"] = t.contiguous().view(torch.int16).numpy().view(np.uint16)
+    else:
+        vec[name] = t.contiguous().numpy()
+
+
+torch.set_num_threads(1)
+g = torch.Generator().manual_seed(0)
+
+with torch.no_grad():
+    # --- RMSNorm, the CPU-runnable baseline configuration (768, eps 1e-6, fp32), cut to 8 rows
+    x = torch.randn(4, 128, 768, generator=g)
+    w = 1 + 0.02 * torch.randn(768, generator=g)
+    m = FastRMSNorm(768, eps=1e-6, use_triton=False)
+    m.weight.copy_(w)
+    xs = x[:1, :8].contiguous()
+    put("rms_f32_x", xs); put("rms_f32_w", w); put("rms_f32_y", m(xs))
+    # bf16 activations and bf16 weight
+    xb = torch.randn(12, 512, generator=g).bfloat16()
+    wb = (1 + 0.02 * torch.randn(512, generator=g)).bfloat16()
+    mb = FastRMSNorm(512, eps=1e-6, use_triton=False).bfloat16()
+    mb.weight.copy_(wb)
+    put("rms_bf16_x", xb); put("rms_bf16_w", wb); put("rms_bf16_y", mb(xb))
+
+    # --- LayerNorm fp32 with affine, bf16 without
+    xl = torch.randn(6, 768, generator=g)
+    wl = 1 + 0.1 * torch.randn(768, generator=g)
+    bl = 0.1 * torch.randn(768, generator=g)
+    ml = FastLayerNorm(768, eps=1e-5, use_triton=False)
+    ml.weight.copy_(wl); ml.bias.copy_(bl)
+    put("ln_f32_x", xl); put("ln_f32_w", wl); put("ln_f32_b", bl); put("ln_f32_y", ml(xl))
+    xlb = torch.randn(16, 320, generator=g).bfloat16()
+    mlb = FastLayerNorm(320, elementwise_affine=False, use_triton=False)
+    put("ln_bf16_x", xlb); put("ln_bf16_y", mlb(xlb))
+
+    # --- RoPE: fp32 tables (built from an fp32 dummy) and bf16 tables (built from q)
+    rope = FastRoPEPositionEmbedding(64, 2048, 10000.0, use_triton=False)
+    q = torch.randn(2, 24, 4, 64, generator=g).bfloat16()
+    k = torch.randn(2, 24, 2, 64, generator=g).bfloat16()
+    cos32, sin32 = rope(torch.empty(0, dtype=torch.float32), seq_len=24)
+    qo, ko = rope.apply_rotary_pos_emb(q, k, cos32, sin32)
+    put("rope_q", q); put("rope_k", k); put("rope_cos_f32", cos32); put("rope_sin_f32", sin32)
+    put("rope_qo_f32tab", qo); put("rope_ko_f32tab", ko)  # fp32 results (type promotion)
+    cosb, sinb = rope(q, seq_len=24)
+    qob, kob = rope.apply_rotary_pos_emb(q, k, cosb, sinb)
+    put("rope_cos", cosb); put("rope_sin", sinb); put("rope_qo", qob); put("rope_ko", kob)
+
+    # --- GLUs, bf16 and fp32
+    xg = torch.randn(12, 2 * 96, generator=g) * 2.0
+    for name, cls in (("swiglu", FastSwiGLU), ("geglu", FastGeGLU), ("reglu", FastReGLU)):
+        mod = cls(96, use_triton=False)
+        put(f"{name}_f32_x", xg); put(f"{name}_f32_y", mod(xg))
+        put(f"{name}_x", xg.bfloat16()); put(f"{name}_y", mod(xg.bfloat16()))
+
+    # --- ALiBi slopes
+    for n in (8, 12, 32):
+        put(f"alibi_slopes_{n}", FastALiBiPositionEmbedding(n, use_triton=False).slopes)
+    put("alibi_bias_4_6", FastALiBiPositionEmbedding(4, use_triton=False)._compute_alibi_pytorch(6, 1))
+
+    # --- attention core (FastBaseAttention._apply_pytorch_attention), fp32 and bf16
+    B, S, H, Hkv, D = 2, 24, 4, 2, 32
+    qa = torch.randn(B, S, H, D, generator=g)
+    ka = torch.randn(B, S, Hkv, D, generator=g)
+    va = torch.randn(B, S, Hkv, D, generator=g)
+    gqa = FastGroupedQueryAttention(H * D, H, Hkv, bias=False, kernel_type="pytorch", causal=True)
+    tile = lambda t: gqa._tile_kv_heads(t.transpose(1, 2), H // Hkv).transpose(1, 2)
+    put("attn_q", qa); put("attn_k", ka); put("attn_v", va)
+    for causal in (False, True):
+        core = FastBaseAttention(H * D, H, kernel_type="pytorch", causal=causal)
+        put(f"attn_out_causal{int(causal)}", core._apply_pytorch_attention(qa, tile(ka), tile(va)))
+        put(f"attn_out_bf16_causal{int(causal)}",
+            core._apply_pytorch_attention(qa.bfloat16(), tile(ka).bfloat16(), tile(va).bfloat16()))
+    # causal + ALiBi bias passed as a 4-D additive mask
+    alibi = FastALiBiPositionEmbedding(H, use_triton=False)
+    bias = alibi._compute_alibi_pytorch(S, B)
+    core = FastBaseAttention(H * D, H, kernel_type="pytorch", causal=True)
+    put("attn_out_alibi", core._apply_pytorch_attention(qa, tile(ka), tile(va), bias.contiguous()))
+    put("attn_tile_order", tile(torch.arange(Hkv).float().view(1, 1, Hkv, 1).expand(1, 1, Hkv, 1)))
+
+    # --- whole GQA module (rope + causal), fp32, PyTorch backend
+    torch.manual_seed(1)
+    mod = FastGroupedQueryAttention(64, 4, 2, bias=False, kernel_type="pytorch", causal=True,
+                                    position_method="rope", max_seq_len=64)
+    xh = torch.randn(2, 16, 64, generator=g)
+    put("gqa_x", xh)
+    for n in ("q_proj", "k_proj", "v_proj", "o_proj"):
+        put(f"gqa_{n}", getattr(mod, n).weight)
+    put("gqa_out", mod(xh)[0])
+
+np.savez_compressed(OUT, **vec)
+print("wrote", OUT, os.path.getsize(OUT), "bytes;", len(vec), "arrays; trinix", trinix.__version__)

@@ -1,0 +1,111 @@
+"""The CPU oracle against vectors produced by the reference itself (tests/golden/).
+
+Same torch ops in the same order, so on the machine that generated the vectors the match is
+bit-exact; the tolerances below only absorb differences between CPU vector units
+(reduction order inside ATen kernels) on other hosts.
+"""
+import pytest
+import torch
+
+from oracle import reference_port as R
+from tests.util import Golden, bf16_ulps
+
+G = Golden()
+F32_TOL = dict(rtol=2e-6, atol=2e-6)
+
+
+def test_rmsnorm_fp32_baseline_config():
+    y = R.rmsnorm_ref(G("rms_f32_x"), G("rms_f32_w"), 1e-6)
+    torch.testing.assert_close(y, G("rms_f32_y"), **F32_TOL)
+
+
+def test_rmsnorm_bf16():
+    y = R.rmsnorm_ref(G("rms_bf16_x"), G("rms_bf16_w"), 1e-6)
+    assert y.dtype == torch.bfloat16
+    assert int(bf16_ulps(y, G("rms_bf16_y")).max()) <= 1
+
+
+def test_rmsnorm_fp32_weight_promotes():
+    y = R.rmsnorm_ref(G("rms_bf16_x"), G("rms_bf16_w").float(), 1e-6)
+    assert y.dtype == torch.float32  # reference behaviour: weight * x.to(input_dtype)
+
+
+def test_layernorm():
+    y = R.layernorm_ref(G("ln_f32_x"), G("ln_f32_w"), G("ln_f32_b"), 1e-5)
+    torch.testing.assert_close(y, G("ln_f32_y"), **F32_TOL)
+    yb = R.layernorm_ref(G("ln_bf16_x"), None, None, 1e-5)
+    assert int(bf16_ulps(yb, G("ln_bf16_y")).max()) <= 1
+
+
+def test_rope_tables_and_rotation():
+    cos32, sin32 = R.rope_tables_ref(64, 24, 10000.0, torch.float32)
+    torch.testing.assert_close(cos32, G("rope_cos_f32"), rtol=0, atol=1e-6)
+    torch.testing.assert_close(sin32, G("rope_sin_f32"), rtol=0, atol=1e-6)
+    qo, ko = R.rope_ref(G("rope_q"), G("rope_k"), G("rope_cos_f32"), G("rope_sin_f32"))
+    assert qo.dtype == torch.float32
+    assert torch.equal(qo, G("rope_qo_f32tab")) and torch.equal(ko, G("rope_ko_f32tab"))
+    qb, kb = R.rope_ref(G("rope_q"), G("rope_k"), G("rope_cos"), G("rope_sin"))
+    assert qb.dtype == torch.bfloat16
+    assert torch.equal(qb, G("rope_qo")) and torch.equal(kb, G("rope_ko"))
+
+
+@pytest.mark.parametrize("name,fn", [("swiglu", R.swiglu_ref), ("geglu", R.geglu_ref),
+                                     ("reglu", R.reglu_ref)])
+def test_glu(name, fn):
+    torch.testing.assert_close(fn(G(f"{name}_f32_x")), G(f"{name}_f32_y"), **F32_TOL)
+    assert int(bf16_ulps(fn(G(f"{name}_x")), G(f"{name}_y")).max()) <= 1
+
+
+def test_alibi():
+    for n in (8, 12, 32):
+        torch.testing.assert_close(R.alibi_slopes_ref(n), G(f"alibi_slopes_{n}"), rtol=1e-7, atol=0)
+    # the benchmark's closed form 2^(-8(i+1)/32) equals the reference's slopes for 32 heads
+    closed = torch.tensor([2.0 ** (-8.0 * (i + 1) / 32) for i in range(32)])
+    torch.testing.assert_close(R.alibi_slopes_ref(32), closed, rtol=1e-6, atol=0)
+    b = R.alibi_bias_ref(R.alibi_slopes_ref(4), 6, 6).unsqueeze(0)
+    torch.testing.assert_close(b, G("alibi_bias_4_6"), rtol=1e-7, atol=0)
+
+
+def test_attention_core_and_kv_tiling():
+    q, k, v = G("attn_q"), G("attn_k"), G("attn_v")
+    order = R.tile_kv_heads_ref(torch.arange(2).float().view(1, 1, 2, 1), 2)
+    assert torch.equal(order, G("attn_tile_order"))
+    kt, vt = R.tile_kv_heads_ref(k, 2), R.tile_kv_heads_ref(v, 2)
+    for causal in (False, True):
+        out = R.attention_ref(q, kt, vt, None, causal)
+        torch.testing.assert_close(out, G(f"attn_out_causal{int(causal)}"), rtol=1e-5, atol=1e-6)
+        ob = R.attention_ref(q.bfloat16(), kt.bfloat16(), vt.bfloat16(), None, causal)
+        assert int(bf16_ulps(ob.contiguous(), G(f"attn_out_bf16_causal{int(causal)}")).max()) <= 2
+    out = R.attention_variant_ref(q, k, v, None, True, None, R.alibi_slopes_ref(4))
+    torch.testing.assert_close(out, G("attn_out_alibi"), rtol=1e-5, atol=1e-6)
+
+
+def test_window_mask_restatement():
+    m = R.window_mask_ref(6, 6, 2, 0)
+    for i in range(6):
+        for j in range(6):
+            visible = -2 <= j - i <= 0
+            assert (m[i, j] == 0) == visible and (m[i, j] == float("-inf")) == (not visible)
+    # window (L, 0) equals causal attention restricted to the last L+1 keys
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(1, 9, 2, 8, generator=g) for _ in range(3))
+    a = R.attention_variant_ref(q, k, v, None, False, (3, 0), None)
+    b = R.attention_variant_ref(q, k, v, None, True, (3, 3), None)
+    torch.testing.assert_close(a, b)
+    assert not torch.isnan(a).any()
+
+
+def test_gqa_module_composition():
+    """decoder pieces composed like FastGroupedQueryAttention.forward (rope + causal)."""
+    x = G("gqa_x")
+    B, S, E = x.shape
+    H, Hkv, D = 4, 2, E // 4
+    import torch.nn.functional as F
+    q = F.linear(x, G("gqa_q_proj")).view(B, S, H, D)
+    k = F.linear(x, G("gqa_k_proj")).view(B, S, Hkv, D)
+    v = F.linear(x, G("gqa_v_proj")).view(B, S, Hkv, D)
+    cos, sin = R.rope_tables_ref(D, S, 10000.0, x.dtype)
+    q, k = R.rope_ref(q, k, cos, sin)
+    a = R.attention_variant_ref(q, k, v, D ** -0.5, True)
+    out = F.linear(a.reshape(B, S, -1), G("gqa_o_proj"))
+    torch.testing.assert_close(out, G("gqa_out"), rtol=1e-5, atol=1e-6)

@@ -1,0 +1,48 @@
+"""Shared helpers for the test-suite: golden vectors, seeded inputs, error metrics."""
+from __future__ import annotations
+
+import os
+
+import numpy as np
+import torch
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_vectors.npz")
+
+
+class Golden:
+    def __init__(self):
+        self._z = np.load(GOLDEN)
+
+    def __call__(self, name: str) -> torch.Tensor:
+        if name + "_bf16" in self._z:
+            bits = self._z[name + "_bf16"]
+            return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16)
+        return torch.from_numpy(self._z[name].copy())
+
+    def has(self, name: str) -> bool:
+        return name in self._z or name + "_bf16" in self._z
+
+
+def rel_err(a: torch.Tensor, b: torch.Tensor, floor_frac: float = 1e-2) -> float:
+    """max |a-b| / max(|b|, floor) with floor = floor_frac * rms(b): the relative error used for
+    the norm / RoPE / GLU tolerance (1e-2 in bf16); the floor keeps near-zero outputs, where
+    an elementwise relative test is ill-conditioned, from dominating."""
+    a, b = a.double().flatten(), b.double().flatten()
+    floor = floor_frac * float(b.pow(2).mean().sqrt()) + 1e-30
+    return float(((a - b).abs() / b.abs().clamp_min(floor)).max())
+
+
+def bf16_ulps(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Distance in bf16 ulps between two bf16 tensors (monotone integer mapping of the bits)."""
+    def key(t):
+        i = t.contiguous().view(torch.int16).to(torch.int32)
+        return torch.where(i < 0, -(i & 0x7FFF), i)
+    return (key(a) - key(b)).abs()
+
+
+def outlier_matrix(rows: int, cols: int, seed: int = 0) -> torch.Tensor:
+    """N(0,1) with 0.1% of the entries scaled x20, as in the int8 benchmark configuration."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, cols, generator=g)
+    mask = torch.rand(rows, cols, generator=g) < 0.001
+    return torch.where(mask, 20 * x, x)

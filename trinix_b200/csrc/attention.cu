@@ -1,0 +1,825 @@
+// Attention forward for sm_100a: softmax(scale * Q K^T + bias) V with online softmax.
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row Q tiles that ping-pong
+// on the tensor pipe. Roles (320 threads):
+//   warps 0-3  softmax group 0 (thread t owns row t of Q tile 0 = TMEM lane t)
+//   warps 4-7  softmax group 1 (Q tile 1)
+//   warp  8    TMA producer: Q once, then K and V tiles through a 4-stage shared-memory ring
+//              (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//   warp  9    MMA issuer: tcgen05.mma kind::f16, S = Q K^T (both operands from shared memory)
+//              and O += P V (P read from TMEM, V from shared memory, MN-major)
+// TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P (16-bit) overwrites the
+// first 64 columns of its S. The softmax groups read S with tcgen05.ld, exponentiate with
+// exp2 (scale*log2e folded into one FMA, ALiBi as one more), write P back with tcgen05.st,
+// rescale O in TMEM only when the running row max grew by more than 2^8 (lazy rescale) and
+// run the epilogue (O / l -> global). KV tiles outside the causal / window range of a Q tile
+// are never visited; masks are applied only on boundary tiles. Query head h reads kv head
+// h / (Hq / Hk), so GQA / MQA need no tiled copies.
+//
+// Every wait on an mbarrier is bounded: after a fixed number of polls the kernel records a
+// code in the status word of the caller's workspace, raises a CTA-wide abort flag, drains its
+// own copies and MMAs (bounded again), frees its TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace trx {
+
+constexpr int ATT_BM = 128;       // rows per Q tile
+constexpr int ATT_BN = 128;       // keys per KV tile
+constexpr int ATT_NQ = 2;         // Q tiles per CTA
+constexpr int ATT_STAGES = 4;     // KV ring depth (K and V tiles alternate)
+constexpr int ATT_THREADS = 320;
+constexpr uint32_t ATT_WAIT_LIMIT = 1u << 26;  // hard cap on polls per wait
+constexpr uint64_t ATT_WAIT_NS = 400ull * 1000 * 1000;  // wall-time budget of one wait
+constexpr float ATT_LAZY_RESCALE = 8.0f;       // log2 units
+
+enum AttnStatus : unsigned {
+  ATT_ST_PRODUCER = 1u,
+  ATT_ST_MMA = 2u,
+  ATT_ST_SOFTMAX = 4u,
+  ATT_ST_DRAIN = 8u,
+};
+
+struct AttnParams {
+  CUtensorMap tm_q;
+  CUtensorMap tm_k;
+  CUtensorMap tm_v;
+  void* out;
+  float* lse;
+  const float* slopes;
+  unsigned int* status;
+  int B, Sq, Sk, Hq;
+  int k_hdiv, v_hdiv;  // query heads per kv head (Hq when the tensor's heads are collapsed)
+  int k_bmul, v_bmul;  // 1, or 0 when the batch dim is broadcast
+  long long o_stride_b, o_stride_s, o_stride_h;
+  long long lse_stride_b, lse_stride_h;
+  float scale_log2;    // softmax scale * log2(e)
+  int causal;
+  int win_left, win_right;  // < 0: no window
+  int is_bf16;
+  int reverse_m;       // schedule the heaviest (last) row blocks first
+};
+
+// ------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up after ATT_WAIT_NS of wall time. Returns false if the CTA is aborting
+// (this wait ran out or another one did); the first to give up records `code` in the status word.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned int* status, unsigned code) {
+#pragma unroll 1
+  for (int fast = 0; fast < 64; ++fast)
+    if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_ns();
+#pragma unroll 1
+  for (uint32_t i = 0; i < ATT_WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (global_ns() - t0 > ATT_WAIT_NS) break;
+    }
+  }
+  *abort_flag = 1;
+  atomicOr(status, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(dst), "l"(tm), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if constexpr (BF16) return Pack<__nv_bfloat16>::pack2(lo, hi);
+  else return Pack<__half>::pack2(lo, hi);
+}
+// 2^x on the special-function unit; 2^-inf = +0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane (base lane + t).
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[N]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[OFF + 0]), "=r"(r[OFF + 1]), "=r"(r[OFF + 2]), "=r"(r[OFF + 3]), "=r"(r[OFF + 4]),
+        "=r"(r[OFF + 5]), "=r"(r[OFF + 6]), "=r"(r[OFF + 7]), "=r"(r[OFF + 8]), "=r"(r[OFF + 9]),
+        "=r"(r[OFF + 10]), "=r"(r[OFF + 11]), "=r"(r[OFF + 12]), "=r"(r[OFF + 13]),
+        "=r"(r[OFF + 14]), "=r"(r[OFF + 15]), "=r"(r[OFF + 16]), "=r"(r[OFF + 17]),
+        "=r"(r[OFF + 18]), "=r"(r[OFF + 19]), "=r"(r[OFF + 20]), "=r"(r[OFF + 21]),
+        "=r"(r[OFF + 22]), "=r"(r[OFF + 23]), "=r"(r[OFF + 24]), "=r"(r[OFF + 25]),
+        "=r"(r[OFF + 26]), "=r"(r[OFF + 27]), "=r"(r[OFF + 28]), "=r"(r[OFF + 29]),
+        "=r"(r[OFF + 30]), "=r"(r[OFF + 31])
+      : "r"(taddr)
+      : "memory");
+}
+template <int OFF, int N>
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[N]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      :
+      : "r"(taddr), "r"(r[OFF + 0]), "r"(r[OFF + 1]), "r"(r[OFF + 2]), "r"(r[OFF + 3]),
+        "r"(r[OFF + 4]), "r"(r[OFF + 5]), "r"(r[OFF + 6]), "r"(r[OFF + 7]), "r"(r[OFF + 8]),
+        "r"(r[OFF + 9]), "r"(r[OFF + 10]), "r"(r[OFF + 11]), "r"(r[OFF + 12]), "r"(r[OFF + 13]),
+        "r"(r[OFF + 14]), "r"(r[OFF + 15]), "r"(r[OFF + 16]), "r"(r[OFF + 17]), "r"(r[OFF + 18]),
+        "r"(r[OFF + 19]), "r"(r[OFF + 20]), "r"(r[OFF + 21]), "r"(r[OFF + 22]), "r"(r[OFF + 23]),
+        "r"(r[OFF + 24]), "r"(r[OFF + 25]), "r"(r[OFF + 26]), "r"(r[OFF + 27]), "r"(r[OFF + 28]),
+        "r"(r[OFF + 29]), "r"(r[OFF + 30]), "r"(r[OFF + 31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field = 1.
+//   K-major operand : rows of 64 16-bit elements (128 B); 8-row groups 1024 B apart (SBO).
+//   MN-major operand: 64 contiguous MN elements per 128-B row of K; 8 K-rows per 1024-B group
+//                     (SBO); the next 64 MN elements start LBO bytes further.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes,
+                                              uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;  // descriptor version
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor for kind::f16 with fp32 accumulation.
+__host__ __device__ constexpr uint32_t make_idesc(int is_bf16, int m, int n, int a_mn_major,
+                                                  int b_mn_major) {
+  return (1u << 4) |                                   // D format fp32
+         (static_cast<uint32_t>(is_bf16 ? 1 : 0) << 7) |   // A format
+         (static_cast<uint32_t>(is_bf16 ? 1 : 0) << 10) |  // B format
+         (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+template <int D>
+struct AttnSmem {
+  static constexpr int CHUNKS = D / 64;              // 64-element (128-byte) column chunks
+  static constexpr int CHUNK_BYTES = ATT_BN * 128;   // 128 rows x 128 B = 16 KB
+  static constexpr int TILE_BYTES = CHUNKS * CHUNK_BYTES;
+  static constexpr int Q_OFF = 0;
+  static constexpr int KV_OFF = ATT_NQ * TILE_BYTES;
+  static constexpr int BAR_OFF = KV_OFF + ATT_STAGES * TILE_BYTES;
+  static constexpr int NUM_BARS = 2 + 2 * ATT_STAGES + 6 + 1;
+  static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 64;
+  static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for 1024-byte alignment
+};
+
+struct TileRange {
+  int jlo, jhi;  // KV tiles [jlo, jhi)
+};
+
+__device__ __forceinline__ TileRange tile_range(const AttnParams& p, int row0) {
+  TileRange r{0, 0};
+  if (row0 >= p.Sq) return r;
+  const int row1 = min(p.Sq, row0 + ATT_BM) - 1;
+  int hi = p.Sk - 1;
+  if (p.causal) hi = min(hi, row1);
+  if (p.win_right >= 0) hi = min(hi, row1 + p.win_right);
+  int lo = 0;
+  if (p.win_left >= 0) lo = max(0, row0 - p.win_left);
+  if (hi < lo) return r;
+  r.jlo = lo / ATT_BN;
+  r.jhi = hi / ATT_BN + 1;
+  return r;
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+    attn_fwd_kernel(const __grid_constant__ AttnParams p) {
+  using L = AttnSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + L::BAR_OFF;
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  // barrier indices
+  constexpr int B_QFULL = 0;                        // [2]
+  constexpr int B_KVFULL = 2;                       // [STAGES]
+  constexpr int B_KVEMPTY = 2 + ATT_STAGES;         // [STAGES]
+  constexpr int B_SFULL = 2 + 2 * ATT_STAGES;       // [2]
+  constexpr int B_PFULL = B_SFULL + 2;              // [2]
+  constexpr int B_ODONE = B_PFULL + 2;              // [2]
+  constexpr int B_DRAIN = B_ODONE + 2;              // [1]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::BAR_OFF + L::NUM_BARS * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  int* fills_issued = reinterpret_cast<int*>(tmem_holder + 2);  // [STAGES]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int mblk = p.reverse_m ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int m0 = mblk * (ATT_NQ * ATT_BM);
+
+  TileRange rng[ATT_NQ];
+#pragma unroll
+  for (int t = 0; t < ATT_NQ; ++t) rng[t] = tile_range(p, m0 + t * ATT_BM);
+  int JLO = 1 << 30, JHI = 0;
+#pragma unroll
+  for (int t = 0; t < ATT_NQ; ++t)
+    if (rng[t].jhi > rng[t].jlo) {
+      JLO = min(JLO, rng[t].jlo);
+      JHI = max(JHI, rng[t].jhi);
+    }
+  if (JHI <= JLO) { JLO = 0; JHI = 0; }
+
+  // A launch that follows a recorded failure does no work: the host must read and clear
+  // the status word first.
+  __shared__ int skip_launch;
+  if (threadIdx.x == 0)
+    skip_launch = (*reinterpret_cast<volatile unsigned int*>(p.status) != 0u) ? 1 : 0;
+  __syncthreads();
+  if (skip_launch) return;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(B_QFULL + 0), 1);
+    mbar_init(bar(B_QFULL + 1), 1);
+    for (int s = 0; s < ATT_STAGES; ++s) {
+      mbar_init(bar(B_KVFULL + s), 1);
+      mbar_init(bar(B_KVEMPTY + s), 1);
+      fills_issued[s] = 0;
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar(B_SFULL + t), 1);
+      mbar_init(bar(B_PFULL + t), ATT_BM);
+      mbar_init(bar(B_ODONE + t), 1);
+    }
+    mbar_init(bar(B_DRAIN), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_holder)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 8) {
+    // =========================== TMA producer =========================================
+    if (lane == 0 && JHI > JLO) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_q) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_k) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_v) : "memory");
+#pragma unroll
+      for (int t = 0; t < ATT_NQ; ++t) {
+        if (rng[t].jhi > rng[t].jlo) {
+          mbar_expect_tx(bar(B_QFULL + t), L::TILE_BYTES);
+#pragma unroll
+          for (int c = 0; c < L::CHUNKS; ++c)
+            tma_load_4d(sbase + L::Q_OFF + t * L::TILE_BYTES + c * L::CHUNK_BYTES, &p.tm_q,
+                        bar(B_QFULL + t), c * 64, m0 + t * ATT_BM, h, b);
+        }
+      }
+      const int hk = h / p.k_hdiv, hv = h / p.v_hdiv;
+      const int bk = b * p.k_bmul, bv = b * p.v_bmul;
+      int fill = 0;
+      bool ok = true;
+      for (int j = JLO; j < JHI && ok; ++j) {
+#pragma unroll
+        for (int kv = 0; kv < 2; ++kv, ++fill) {
+          const int s = fill % ATT_STAGES;
+          const uint32_t par = ((fill / ATT_STAGES) & 1) ^ 1;
+          ok = mbar_wait(bar(B_KVEMPTY + s), par, abort_flag, p.status, ATT_ST_PRODUCER);
+          if (!ok) break;
+          mbar_expect_tx(bar(B_KVFULL + s), L::TILE_BYTES);
+          fills_issued[s] = fill / ATT_STAGES + 1;
+          const CUtensorMap* tm = kv == 0 ? &p.tm_k : &p.tm_v;
+#pragma unroll
+          for (int c = 0; c < L::CHUNKS; ++c)
+            tma_load_4d(sbase + L::KV_OFF + s * L::TILE_BYTES + c * L::CHUNK_BYTES, tm,
+                        bar(B_KVFULL + s), c * 64, j * ATT_BN, kv == 0 ? hk : hv,
+                        kv == 0 ? bk : bv);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // =========================== MMA issuer ===========================================
+    if (lane == 0 && JHI > JLO) {
+      const uint32_t idesc_qk = make_idesc(BF16 ? 1 : 0, ATT_BM, ATT_BN, 0, 0);
+      const uint32_t idesc_pv = make_idesc(BF16 ? 1 : 0, ATT_BM, D, 0, 1);
+      bool ok = true;
+      bool q_ready[ATT_NQ] = {false, false};
+      int it[ATT_NQ] = {0, 0};  // softmax iterations issued per Q tile
+      auto active = [&](int t, int j) { return j >= rng[t].jlo && j < rng[t].jhi; };
+      auto kv_wait = [&](int fill) {
+        return mbar_wait(bar(B_KVFULL + fill % ATT_STAGES), (fill / ATT_STAGES) & 1, abort_flag,
+                         p.status, ATT_ST_MMA);
+      };
+      auto issue_qk = [&](int t, int fill) {
+        if (!q_ready[t]) {
+          if (!mbar_wait(bar(B_QFULL + t), 0, abort_flag, p.status, ATT_ST_MMA)) return false;
+          q_ready[t] = true;
+        }
+        tc_fence_after();
+        const uint32_t qa = sbase + L::Q_OFF + t * L::TILE_BYTES;
+        const uint32_t ka = sbase + L::KV_OFF + (fill % ATT_STAGES) * L::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * L::CHUNK_BYTES + (kk % 4) * 32;
+          mma_ss(tmem_base + t * ATT_BN, make_desc(qa + off, 16, 1024),
+                 make_desc(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(bar(B_SFULL + t));
+        return true;
+      };
+      auto issue_pv = [&](int t, int fill, bool accumulate) {
+        if (!mbar_wait(bar(B_PFULL + t), it[t] & 1, abort_flag, p.status, ATT_ST_MMA))
+          return false;
+        tc_fence_after();
+        const uint32_t va = sbase + L::KV_OFF + (fill % ATT_STAGES) * L::TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < ATT_BN / 16; ++kk) {
+          mma_ts(tmem_base + 2 * ATT_BN + t * ATT_BN, tmem_base + t * ATT_BN + kk * 8,
+                 make_desc(va + kk * 2048, L::CHUNK_BYTES, 1024), idesc_pv,
+                 (accumulate || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(bar(B_ODONE + t));
+        ++it[t];
+        return true;
+      };
+
+      // prologue: S(JLO)
+      ok = kv_wait(0);
+      for (int t = 0; t < ATT_NQ && ok; ++t)
+        if (active(t, JLO)) ok = issue_qk(t, 0);
+      if (ok) tc_commit(bar(B_KVEMPTY + 0));
+      for (int j = JLO; j < JHI && ok; ++j) {
+        const int fill_v = 2 * (j - JLO) + 1;
+        const int fill_kn = fill_v + 1;
+        ok = kv_wait(fill_v);
+        bool kn_waited = false;
+        for (int t = 0; t < ATT_NQ && ok; ++t) {
+          if (active(t, j)) ok = issue_pv(t, fill_v, j > rng[t].jlo);
+          if (ok && j + 1 < JHI && active(t, j + 1)) {
+            if (!kn_waited) {
+              ok = kv_wait(fill_kn);
+              kn_waited = true;
+            }
+            if (ok) ok = issue_qk(t, fill_kn);
+          }
+        }
+        if (!ok) break;
+        tc_commit(bar(B_KVEMPTY + fill_v % ATT_STAGES));
+        if (j + 1 < JHI) {
+          if (!kn_waited) ok = kv_wait(fill_kn);
+          if (ok) tc_commit(bar(B_KVEMPTY + fill_kn % ATT_STAGES));
+        }
+      }
+      if (!ok) {
+        // drain whatever was issued before giving up
+        tc_commit(bar(B_DRAIN));
+        const uint64_t t0 = global_ns();
+        while (!mbar_try_wait(bar(B_DRAIN), 0) && global_ns() - t0 < ATT_WAIT_NS) {
+        }
+      }
+    }
+  } else {
+    // =========================== softmax groups =======================================
+    const int t = warp >> 2;                 // Q tile of this group
+    const int r = threadIdx.x & (ATT_BM - 1);  // row within the tile == TMEM lane
+    const int row = m0 + t * ATT_BM + r;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_base + t * ATT_BN;
+    const uint32_t o_addr = tmem_base + lane_base + 2 * ATT_BN + t * ATT_BN;
+    const int n_it = rng[t].jhi - rng[t].jlo;
+
+    // visible key range of this row: lo_i <= col <= hi_i
+    int hi_i = p.Sk - 1, lo_i = 0;
+    if (p.causal) hi_i = min(hi_i, row);
+    if (p.win_right >= 0) hi_i = min(hi_i, row + p.win_right);
+    if (p.win_left >= 0) lo_i = max(0, row - p.win_left);
+    // tile-level: rows [row0, row1] of this Q tile
+    const int row0 = m0 + t * ATT_BM;
+    const int row1 = min(p.Sq, row0 + ATT_BM) - 1;
+    int hi_min = p.Sk - 1, lo_max = 0;
+    if (p.causal) hi_min = min(hi_min, row0);
+    if (p.win_right >= 0) hi_min = min(hi_min, row0 + p.win_right);
+    if (p.win_left >= 0) lo_max = max(0, row1 - p.win_left);
+
+    const float sl2 = p.scale_log2;
+    const float slope2 = p.slopes ? p.slopes[h] * 1.4426950408889634f : 0.0f;
+    const bool has_alibi = p.slopes != nullptr;
+
+    float m_run = -INFINITY;  // reference max (log2 domain) used for exponentiation
+    float l_run = 0.0f;
+    bool ok = true;
+
+    for (int itn = 0; itn < n_it && ok; ++itn) {
+      const int j = rng[t].jlo + itn;
+      const int c0 = j * ATT_BN;
+      ok = __all_sync(0xffffffffu,
+                      mbar_wait(bar(B_SFULL + t), itn & 1, abort_flag, p.status, ATT_ST_SOFTMAX));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sr[ATT_BN];
+      tmem_ld32<0>(s_addr + 0, sr);
+      tmem_ld32<32>(s_addr + 32, sr);
+      tmem_ld32<64>(s_addr + 64, sr);
+      tmem_ld32<96>(s_addr + 96, sr);
+      tmem_wait_ld();
+
+      const bool need_mask = (c0 + ATT_BN - 1 > hi_min) || (c0 < lo_max);
+      const bool general = need_mask || has_alibi || !(sl2 > 0.0f);
+      float m_tile = -INFINITY;
+      if (general) {
+        const float fi = static_cast<float>(row - c0);
+#pragma unroll
+        for (int c = 0; c < ATT_BN; ++c) {
+          float x = __uint_as_float(sr[c]) * sl2;
+          if (has_alibi) x = fmaf(-slope2, fabsf(fi - static_cast<float>(c)), x);
+          if (need_mask) {
+            const int col = c0 + c;
+            if (col < lo_i || col > hi_i) x = -INFINITY;
+          }
+          sr[c] = __float_as_uint(x);
+          m_tile = fmaxf(m_tile, x);
+        }
+      } else {
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < ATT_BN; c += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sr[c + 0]));
+          mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
+        }
+        m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+      }
+
+      // lazy rescale: keep the old reference max unless the new one is much larger
+      float factor = 1.0f;
+      bool rescale = false;
+      if (m_tile > m_run + ATT_LAZY_RESCALE || (m_run == -INFINITY && m_tile > -INFINITY)) {
+        factor = fast_exp2(m_run - m_tile);  // 0 when m_run == -inf
+        rescale = (itn > 0);
+        m_run = m_tile;
+        l_run *= factor;
+      }
+      const float m_ref = (m_run == -INFINITY) ? 0.0f : m_run;
+
+      // P = exp2(x - m_ref), packed to 16-bit pairs in place (sr[0..63])
+      float2 lsum = make_float2(0.0f, 0.0f);
+      if (general) {
+#pragma unroll
+        for (int c = 0; c < ATT_BN; c += 2) {
+          const float p0 = fast_exp2(__uint_as_float(sr[c]) - m_ref);
+          const float p1 = fast_exp2(__uint_as_float(sr[c + 1]) - m_ref);
+          lsum.x += p0;
+          lsum.y += p1;
+          sr[c / 2] = pack16<BF16>(p0, p1);
+        }
+      } else {
+        const float2 sc2 = make_float2(sl2, sl2);
+        const float2 nm2 = make_float2(-m_ref, -m_ref);
+#pragma unroll
+        for (int c = 0; c < ATT_BN; c += 2) {
+          const float2 x =
+              fma2(make_float2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2, nm2);
+          const float2 pe = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          lsum = add2(lsum, pe);
+          sr[c / 2] = pack16<BF16>(pe.x, pe.y);
+        }
+      }
+      l_run += lsum.x + lsum.y;
+
+      tmem_st32<0>(s_addr + 0, sr);
+      tmem_st32<32>(s_addr + 32, sr);
+
+      // O rescale (rare after the first tiles): needs the previous PV of this tile done
+      if (__any_sync(0xffffffffu, rescale)) {
+        ok = __all_sync(0xffffffffu, mbar_wait(bar(B_ODONE + t), (itn - 1) & 1, abort_flag,
+                                               p.status, ATT_ST_SOFTMAX));
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int cc = 0; cc < D; cc += 32) {
+            uint32_t orr[32];
+            tmem_ld32<0>(o_addr + cc, orr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              orr[e] = __float_as_uint(__uint_as_float(orr[e]) * factor);
+            tmem_st32<0>(o_addr + cc, orr);
+          }
+        }
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(B_PFULL + t));
+    }
+
+    // ---- epilogue: O / l -> global --------------------------------------------------
+    if (ok && n_it > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait(bar(B_ODONE + t), (n_it - 1) & 1, abort_flag,
+                                             p.status, ATT_ST_SOFTMAX));
+      tc_fence_after();
+    }
+    if (ok) {
+      const float inv = (n_it > 0 && l_run > 0.0f) ? __fdividef(1.0f, l_run) : 0.0f;
+      uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
+                      2ll * (b * p.o_stride_b + static_cast<long long>(row) * p.o_stride_s +
+                             h * p.o_stride_h);
+#pragma unroll
+      for (int cc = 0; cc < D; cc += 32) {
+        uint32_t orr[32];
+        if (n_it > 0) {
+          tmem_ld32<0>(o_addr + cc, orr);  // warp-collective: executed by every lane
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) orr[e] = 0u;
+        }
+        if (row < p.Sq) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 v;
+            uint32_t* vv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float a0 = __uint_as_float(orr[e + 2 * q]) * inv;
+              const float a1 = __uint_as_float(orr[e + 2 * q + 1]) * inv;
+              vv[q] = pack16<BF16>(a0, a1);
+            }
+            *reinterpret_cast<uint4*>(orow + 2 * (cc + e)) = v;
+          }
+        }
+      }
+      if (p.lse && row < p.Sq) {
+        const float lse = (n_it > 0 && l_run > 0.0f)
+                              ? (m_run + log2f(l_run)) * 0.6931471805599453f
+                              : -INFINITY;
+        p.lse[b * p.lse_stride_b + h * p.lse_stride_h + row] = lse;
+      }
+    }
+  }
+
+  // ------------------------------- teardown -------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // make sure no bulk copy of this CTA is still in flight before shared memory is released
+    for (int s = 0; s < ATT_STAGES; ++s) {
+      const int n = fills_issued[s];
+      if (n > 0) {
+        bool done = false;
+        const uint64_t t0 = global_ns();
+        while (!(done = mbar_try_wait(bar(B_KVFULL + s), (n - 1) & 1)) &&
+               global_ns() - t0 < ATT_WAIT_NS) {
+        }
+        if (!done) atomicOr(p.status, ATT_ST_DRAIN);
+      }
+    }
+    for (int t = 0; t < ATT_NQ; ++t)
+      if (rng[t].jhi > rng[t].jlo) {
+        bool done = false;
+        const uint64_t t0 = global_ns();
+        while (!(done = mbar_try_wait(bar(B_QFULL + t), 0)) && global_ns() - t0 < ATT_WAIT_NS) {
+        }
+        if (!done) atomicOr(p.status, ATT_ST_DRAIN);
+      }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(512u)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// (D, S, H, B) view of a (B, S, H, D) tensor with element strides (b, s, h); box = 64 x 128.
+// Dims with stride 0 (broadcast) are collapsed to size 1 by the caller.
+static int make_map(CUtensorMap* tm, const void* base, int is_bf16, int64_t D, int64_t S,
+                    int64_t H, int64_t B, int64_t sb, int64_t ss, int64_t sh) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return TRX_ERR_CUDA;
+  if (!aligned_to(base, 16)) return TRX_ERR_ALIGNMENT;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S),
+                        static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
+  // size-1 dims may carry any stride; give them a legal one
+  if (S == 1) ss = D;
+  if (H == 1) sh = ss * S;
+  if (B == 1) sb = (sh * H > ss * S) ? sh * H : ss * S;
+  if (ss < D || sh <= 0 || sb <= 0) return TRX_ERR_STRIDE;
+  if ((ss * 2) % 16 || (sh * 2) % 16 || (sb * 2) % 16) return TRX_ERR_ALIGNMENT;
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(ss * 2), static_cast<cuuint64_t>(sh * 2),
+                           static_cast<cuuint64_t>(sb * 2)};
+  for (int i = 0; i < 3; ++i)
+    if (strides[i] >= (1ull << 40)) return TRX_ERR_STRIDE;
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(ATT_BM), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                   4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? TRX_OK : TRX_ERR_CUDA;
+}
+
+template <int D, bool BF16>
+static int launch_attn(const AttnParams& p, cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return TRX_ERR_CUDA;
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             AttnSmem<D>::DYN_BYTES) != cudaSuccess)
+      return TRX_ERR_CUDA;
+    configured[dev] = true;
+  }
+  const int mblocks = (p.Sq + ATT_NQ * ATT_BM - 1) / (ATT_NQ * ATT_BM);
+  dim3 grid(mblocks, p.Hq, p.B);
+  attn_fwd_kernel<D, BF16><<<grid, ATT_THREADS, AttnSmem<D>::DYN_BYTES, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? TRX_OK : TRX_ERR_CUDA;
+}
+
+}  // namespace trx
+
+using namespace trx;
+
+extern "C" size_t trx_attn_workspace_bytes(void) { return 256; }
+
+extern "C" int trx_attn_fwd(const void* q, const void* k, const void* v, void* out,
+                            float* lse_or_null, const float* slopes_or_null, int64_t B, int64_t Sq,
+                            int64_t Sk, int64_t Hq, int64_t Hk, int64_t D,
+                            const int64_t q_strides[3], const int64_t k_strides[3],
+                            const int64_t v_strides[3], const int64_t o_strides[3], float scale,
+                            int causal, int64_t window_left, int64_t window_right, int dtype,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+  if (dtype != TRX_BF16 && dtype != TRX_F16) return TRX_ERR_DTYPE;
+  if (B < 0 || Sq < 0 || Sk < 0 || Hq <= 0 || Hk <= 0 || D <= 0) return TRX_ERR_SHAPE;
+  if (Hq % Hk != 0) return TRX_ERR_SHAPE;
+  if (D != 64 && D != 128) return TRX_ERR_UNSUPPORTED;
+  if ((window_left < 0) != (window_right < 0)) return TRX_ERR_SHAPE;
+  if (B == 0 || Sq == 0) return TRX_OK;
+  if (!q || !out || !q_strides || !k_strides || !v_strides || !o_strides)
+    return TRX_ERR_NULL_POINTER;
+  if (Sk > 0 && (!k || !v)) return TRX_ERR_NULL_POINTER;
+  if (!workspace) return TRX_ERR_WORKSPACE;
+  if (workspace_bytes < trx_attn_workspace_bytes() || !aligned_to(workspace, 16))
+    return TRX_ERR_WORKSPACE;
+  if (Sq >= (1ll << 30) || Sk >= (1ll << 30) || Hq > 65535 || B > 65535)
+    return TRX_ERR_SHAPE;
+  if (!aligned_to(out, 16) || o_strides[0] % 8 || o_strides[1] % 8 || o_strides[2] % 8)
+    return TRX_ERR_ALIGNMENT;
+  for (int i = 0; i < 3; ++i)
+    if (q_strides[i] < 0 || k_strides[i] < 0 || v_strides[i] < 0 || o_strides[i] < 0)
+      return TRX_ERR_STRIDE;
+
+  AttnParams p{};
+  const int is_bf16 = dtype == TRX_BF16;
+  int rc = make_map(&p.tm_q, q, is_bf16, D, Sq, Hq, B, q_strides[0], q_strides[1], q_strides[2]);
+  if (rc != TRX_OK) return rc;
+  // Broadcast (stride-0) head or batch dims of k / v collapse to extent 1.
+  const int64_t Sk_map = Sk > 0 ? Sk : 1;
+  const void* kk = Sk > 0 ? k : q;
+  const void* vv = Sk > 0 ? v : q;
+  const bool k_hb = (Hk > 1 && k_strides[2] == 0), v_hb = (Hk > 1 && v_strides[2] == 0);
+  const bool k_bb = (B > 1 && k_strides[0] == 0), v_bb = (B > 1 && v_strides[0] == 0);
+  rc = make_map(&p.tm_k, kk, is_bf16, D, Sk_map, k_hb ? 1 : Hk, k_bb ? 1 : B, k_strides[0],
+                k_strides[1], k_strides[2]);
+  if (rc != TRX_OK) return rc;
+  rc = make_map(&p.tm_v, vv, is_bf16, D, Sk_map, v_hb ? 1 : Hk, v_bb ? 1 : B, v_strides[0],
+                v_strides[1], v_strides[2]);
+  if (rc != TRX_OK) return rc;
+  p.out = out;
+  p.lse = lse_or_null;
+  p.slopes = slopes_or_null;
+  p.status = reinterpret_cast<unsigned int*>(workspace);
+  p.B = static_cast<int>(B);
+  p.Sq = static_cast<int>(Sq);
+  p.Sk = static_cast<int>(Sk);
+  p.Hq = static_cast<int>(Hq);
+  const int group = static_cast<int>(Hq / Hk);
+  p.k_hdiv = k_hb ? static_cast<int>(Hq) : group;
+  p.v_hdiv = v_hb ? static_cast<int>(Hq) : group;
+  p.k_bmul = k_bb ? 0 : 1;
+  p.v_bmul = v_bb ? 0 : 1;
+  p.o_stride_b = o_strides[0];
+  p.o_stride_s = o_strides[1];
+  p.o_stride_h = o_strides[2];
+  p.lse_stride_b = Hq * Sq;
+  p.lse_stride_h = Sq;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal ? 1 : 0;
+  p.win_left = window_left < 0 ? -1 : static_cast<int>(window_left > (1ll << 29) ? (1ll << 29) : window_left);
+  p.win_right = window_right < 0 ? -1 : static_cast<int>(window_right > (1ll << 29) ? (1ll << 29) : window_right);
+  p.is_bf16 = is_bf16;
+  p.reverse_m = causal ? 1 : 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 128) return is_bf16 ? launch_attn<128, true>(p, s) : launch_attn<128, false>(p, s);
+  return is_bf16 ? launch_attn<64, true>(p, s) : launch_attn<64, false>(p, s);
+}

@@ -1,0 +1,444 @@
+// Row kernels: RMSNorm, LayerNorm, per-row int8 quantise, fused RMSNorm -> int8.
+//
+// One skeleton serves the four ops. A row is read from HBM exactly once with
+// 128-bit streaming loads and then lives in registers (VPT 16-byte vectors per
+// thread, TPR threads per row); statistics are reduced with warp shuffles
+// (plus one shared-memory hop when a row spans more than one warp), and the
+// result is produced from the registers — the row is never re-read.
+//   TPR == 32 : one warp per row, 8 rows per 256-thread CTA, no barriers at all.
+//   TPR  > 32 : one CTA per row.
+// CTAs are persistent: the grid is sized to what the 148 SMs can hold and
+// strides over the rows. Rows that do not fit the vector path (columns not a
+// multiple of the vector width, unaligned pointers, more than 16384 vectors)
+// take a scalar multi-pass kernel, so nothing is ever truncated.
+#include "common.cuh"
+
+namespace trx {
+
+enum RowOp { OP_RMSNORM = 0, OP_LAYERNORM = 1, OP_QUANT = 2, OP_RMSNORM_QUANT = 3 };
+
+struct RowParams {
+  const void* x;
+  const void* w;
+  const void* b;
+  void* y;
+  int8_t* codes;
+  float* scales;
+  float* mean;
+  float* rstd;
+  int64_t R;
+  int64_t C;
+  int64_t x_stride;      // elements
+  int64_t y_stride;      // elements
+  int64_t codes_stride;  // bytes == elements
+  float eps;
+  int w_dtype;
+};
+
+// Packed product of two 16-bit pairs with one rounding per lane.
+template <typename T>
+__device__ __forceinline__ uint32_t mul_packed16(uint32_t a, uint32_t b);
+template <>
+__device__ __forceinline__ uint32_t mul_packed16<__nv_bfloat16>(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r =
+      __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <>
+__device__ __forceinline__ uint32_t mul_packed16<__half>(uint32_t a, uint32_t b) {
+  const __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <>
+__device__ __forceinline__ uint32_t mul_packed16<float>(uint32_t a, uint32_t) {
+  return a;  // never used: fp32 rows take the scalar-lane path
+}
+
+template <int OP, typename T, int TPR, int VPT>
+__global__ void __launch_bounds__((TPR > 32 ? TPR : 256))
+    row_kernel(const RowParams p) {
+  using P = Pack<T>;
+  constexpr int VEC = P::VEC;
+  constexpr int BLOCK = TPR > 32 ? TPR : 256;
+  constexpr int ROWS_PER_CTA = BLOCK / TPR;
+  constexpr bool HAS_NORM = (OP == OP_RMSNORM || OP == OP_LAYERNORM || OP == OP_RMSNORM_QUANT);
+  constexpr bool HAS_QUANT = (OP == OP_QUANT || OP == OP_RMSNORM_QUANT);
+
+  __shared__ float red[2][32];
+  int sel = 0;
+
+  const int t = threadIdx.x % TPR;
+  const int row_in_cta = threadIdx.x / TPR;
+  const int nvec = static_cast<int>(p.C / VEC);
+
+  for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * ROWS_PER_CTA; row0 < p.R;
+       row0 += static_cast<int64_t>(gridDim.x) * ROWS_PER_CTA) {
+    const int64_t row = row0 + row_in_cta;
+    const bool row_ok = row < p.R;
+    if (TPR == 32 && !row_ok) continue;  // warp-uniform; no barriers on this path
+
+    // ---- 1. the one and only HBM read of the row --------------------------------
+    uint4 raw[VPT];
+    const T* xrow = reinterpret_cast<const T*>(p.x) + (row_ok ? row : 0) * p.x_stride;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = i * TPR + t;
+      raw[i] = (row_ok && v < nvec) ? ld_stream16(xrow + static_cast<int64_t>(v) * VEC)
+                                    : make_uint4(0u, 0u, 0u, 0u);
+    }
+
+    float mean = 0.0f, rstd = 1.0f;
+    // ---- 2. statistics -------------------------------------------------------------
+    if constexpr (OP == OP_RMSNORM || OP == OP_RMSNORM_QUANT) {
+      float2 ss2 = make_float2(0.0f, 0.0f);
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        float2 f2[VEC / 2];
+        P::unpack2(raw[i], f2);
+#pragma unroll
+        for (int j = 0; j < VEC / 2; ++j) ss2 = fma2(f2[j], f2[j], ss2);
+      }
+      float ss = row_reduce<TPR, false>(ss2.x + ss2.y, red, sel);
+      const float var = __fdiv_rn(ss, static_cast<float>(p.C));
+      rstd = __fdiv_rn(1.0f, __fsqrt_rn(var + p.eps));
+    } else if constexpr (OP == OP_LAYERNORM) {
+      float s = 0.0f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        float f[VEC];
+        P::unpack(raw[i], f);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) s += f[j];
+      }
+      s = row_reduce<TPR, false>(s, red, sel);
+      mean = __fdiv_rn(s, static_cast<float>(p.C));
+      float cs = 0.0f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = i * TPR + t;
+        if (v < nvec) {
+          float f[VEC];
+          P::unpack(raw[i], f);
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) {
+            const float d = f[j] - mean;
+            cs = fmaf(d, d, cs);
+          }
+        }
+      }
+      cs = row_reduce<TPR, false>(cs, red, sel);
+      const float var = __fdiv_rn(cs, static_cast<float>(p.C));
+      rstd = __fdiv_rn(1.0f, __fsqrt_rn(var + p.eps));
+    }
+    if constexpr (HAS_NORM) {
+      if (row_ok && t == 0) {
+        if (p.rstd) p.rstd[row] = rstd;
+        if (OP == OP_LAYERNORM && p.mean) p.mean[row] = mean;
+      }
+    }
+
+    // ---- 3. normalise (registers -> registers, or registers -> HBM) ----------------
+    if constexpr (HAS_NORM) {
+      T* yrow = (OP == OP_RMSNORM_QUANT)
+                    ? nullptr
+                    : reinterpret_cast<T*>(p.y) + (row_ok ? row : 0) * p.y_stride;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = i * TPR + t;
+        if (row_ok && v < nvec) {
+          float f[VEC];
+          P::unpack(raw[i], f);
+          const int64_t col = static_cast<int64_t>(v) * VEC;
+          if constexpr (OP == OP_LAYERNORM) {
+            float wv[VEC], bv[VEC];
+            if (p.w) load_param_vec<VEC>(p.w, p.w_dtype, col, wv);
+            if (p.b) load_param_vec<VEC>(p.b, p.w_dtype, col, bv);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) {
+              float o = (f[j] - mean) * rstd;
+              if (p.w) o *= wv[j];
+              if (p.b) o += bv[j];
+              f[j] = o;
+            }
+          } else {
+            // round(x * rstd) to the activation dtype, then times w, then round again:
+            // the order of the reference's PyTorch backend.
+            if constexpr (VEC == 8) {
+              if (p.w_dtype == P::DTYPE) {
+                // Same 16-bit dtype on both sides: the second product is a single packed
+                // multiply with one rounding (the exact product fits in fp32).
+                const uint4 wraw = ld_cached16(reinterpret_cast<const T*>(p.w) + col);
+                const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wraw);
+                uint32_t yu[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint32_t n2 =
+                      P::pack2(__fmul_rn(f[2 * j], rstd), __fmul_rn(f[2 * j + 1], rstd));
+                  yu[j] = mul_packed16<T>(wu[j], n2);
+                }
+                const uint4 packed16 = make_uint4(yu[0], yu[1], yu[2], yu[3]);
+                if constexpr (OP == OP_RMSNORM_QUANT) {
+                  raw[i] = packed16;
+                } else {
+                  st_stream16(yrow + col, packed16);
+                }
+                continue;
+              }
+            }
+            float wv[VEC];
+            load_param_vec<VEC>(p.w, p.w_dtype, col, wv);
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) {
+              f[j] = __fmul_rn(wv[j], P::round(__fmul_rn(f[j], rstd)));
+            }
+          }
+          const uint4 packed = P::pack(f);
+          if constexpr (OP == OP_RMSNORM_QUANT) {
+            raw[i] = packed;
+          } else {
+            st_stream16(yrow + col, packed);
+          }
+        }
+      }
+    }
+
+    // ---- 4. quantise the (possibly normalised) row held in registers ----------------
+    if constexpr (HAS_QUANT) {
+      typename P::AbsAcc acc = P::absacc_init();
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) P::absacc(raw[i], acc);  // padding vectors are zero
+      const float am = row_reduce<TPR, true>(P::absacc_final(acc), red, sel);
+      const QuantRow qr = make_quant_row(am);
+      if (row_ok && t == 0) p.scales[row] = qr.scale;
+      int8_t* crow = p.codes + (row_ok ? row : 0) * p.codes_stride;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = i * TPR + t;
+        if (row_ok && v < nvec) {
+          float2 f2[VEC / 2];
+          P::unpack2(raw[i], f2);
+          uint32_t yb[VEC];
+#pragma unroll
+          for (int j = 0; j < VEC / 2; ++j) quant_pair(f2[j], qr, yb[2 * j], yb[2 * j + 1]);
+          int8_t* dst = crow + static_cast<int64_t>(v) * VEC;
+          if constexpr (VEC == 8) {
+            st_stream8(dst, make_uint2(pack_low_bytes(yb[0], yb[1], yb[2], yb[3]),
+                                       pack_low_bytes(yb[4], yb[5], yb[6], yb[7])));
+          } else {
+            st_stream4(dst, pack_low_bytes(yb[0], yb[1], yb[2], yb[3]));
+          }
+        }
+      }
+    }
+  }
+}
+
+// Scalar multi-pass fallback: one CTA per row, any C, any alignment. The row is
+// re-read from global memory (L2-resident after the first pass).
+template <int OP, typename T>
+__global__ void __launch_bounds__(256) row_kernel_generic(const RowParams p) {
+  using P = Pack<T>;
+  __shared__ float red[2][32];
+  int sel = 0;
+  constexpr bool HAS_QUANT = (OP == OP_QUANT || OP == OP_RMSNORM_QUANT);
+  for (int64_t row = blockIdx.x; row < p.R; row += gridDim.x) {
+    const T* xrow = reinterpret_cast<const T*>(p.x) + row * p.x_stride;
+    float mean = 0.0f, rstd = 1.0f;
+    if constexpr (OP == OP_RMSNORM || OP == OP_RMSNORM_QUANT) {
+      float ss = 0.0f;
+      for (int64_t c = threadIdx.x; c < p.C; c += 256) {
+        const float f = P::load1(xrow + c);
+        ss = fmaf(f, f, ss);
+      }
+      ss = row_reduce<256, false>(ss, red, sel);
+      rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(ss, static_cast<float>(p.C)) + p.eps));
+    } else if constexpr (OP == OP_LAYERNORM) {
+      float s = 0.0f;
+      for (int64_t c = threadIdx.x; c < p.C; c += 256) s += P::load1(xrow + c);
+      s = row_reduce<256, false>(s, red, sel);
+      mean = __fdiv_rn(s, static_cast<float>(p.C));
+      float cs = 0.0f;
+      for (int64_t c = threadIdx.x; c < p.C; c += 256) {
+        const float d = P::load1(xrow + c) - mean;
+        cs = fmaf(d, d, cs);
+      }
+      cs = row_reduce<256, false>(cs, red, sel);
+      rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(cs, static_cast<float>(p.C)) + p.eps));
+    }
+    if (OP != OP_QUANT && threadIdx.x == 0) {
+      if (p.rstd) p.rstd[row] = rstd;
+      if (OP == OP_LAYERNORM && p.mean) p.mean[row] = mean;
+    }
+    auto normed = [&](int64_t c) -> float {
+      const float f = P::load1(xrow + c);
+      if constexpr (OP == OP_LAYERNORM) {
+        float o = (f - mean) * rstd;
+        if (p.w) o *= load_param1(p.w, p.w_dtype, c);
+        if (p.b) o += load_param1(p.b, p.w_dtype, c);
+        return P::round(o);
+      } else if constexpr (OP == OP_QUANT) {
+        return f;
+      } else {
+        return P::round(
+            __fmul_rn(load_param1(p.w, p.w_dtype, c), P::round(__fmul_rn(f, rstd))));
+      }
+    };
+    if constexpr (!HAS_QUANT) {
+      T* yrow = reinterpret_cast<T*>(p.y) + row * p.y_stride;
+      for (int64_t c = threadIdx.x; c < p.C; c += 256) P::store1(yrow + c, normed(c));
+    } else {
+      float am = 0.0f;
+      for (int64_t c = threadIdx.x; c < p.C; c += 256) am = fmaxf(am, fabsf(normed(c)));
+      am = row_reduce<256, true>(am, red, sel);
+      const float scale = __fdiv_rn(am, 127.0f);
+      if (threadIdx.x == 0) p.scales[row] = scale;
+      int8_t* crow = p.codes + row * p.codes_stride;
+      for (int64_t c = threadIdx.x; c < p.C; c += 256)
+        crow[c] = static_cast<int8_t>(quant_code(normed(c), scale));
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Host-side dispatch
+// ----------------------------------------------------------------------------
+static int sm_count_of_current_device() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+template <int OP, typename T, int TPR, int VPT>
+static int launch_cfg(const RowParams& p, cudaStream_t stream) {
+  constexpr int BLOCK = TPR > 32 ? TPR : 256;
+  constexpr int ROWS_PER_CTA = BLOCK / TPR;
+  static int blocks_per_sm = 0;  // same for every sm_100a device
+  if (blocks_per_sm == 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, row_kernel<OP, T, TPR, VPT>, BLOCK, 0) !=
+            cudaSuccess ||
+        n <= 0)
+      n = 1;
+    blocks_per_sm = n;
+  }
+  const int64_t need = (p.R + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
+  const int64_t cap = static_cast<int64_t>(sm_count_of_current_device()) * blocks_per_sm;
+  const unsigned grid = static_cast<unsigned>(need < cap ? need : cap);
+  row_kernel<OP, T, TPR, VPT><<<grid, BLOCK, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? TRX_OK : TRX_ERR_CUDA;
+}
+
+template <int OP, typename T>
+static int launch_row(const RowParams& p, cudaStream_t stream) {
+  constexpr int VEC = Pack<T>::VEC;
+  if (p.R == 0) return TRX_OK;
+  constexpr bool HAS_QUANT = (OP == OP_QUANT || OP == OP_RMSNORM_QUANT);
+  constexpr bool WRITES_Y = (OP == OP_RMSNORM || OP == OP_LAYERNORM);
+  bool vec_ok = (p.C % VEC == 0) && aligned_to(p.x, 16) && (p.x_stride % VEC == 0);
+  if (WRITES_Y) vec_ok = vec_ok && aligned_to(p.y, 16) && (p.y_stride % VEC == 0);
+  if (HAS_QUANT) vec_ok = vec_ok && aligned_to(p.codes, VEC) && (p.codes_stride % VEC == 0);
+  if (p.w) vec_ok = vec_ok && aligned_to(p.w, 16);
+  if (p.b) vec_ok = vec_ok && aligned_to(p.b, 16);
+  const int64_t nvec = p.C / VEC;
+  if (vec_ok && nvec <= 16384) {
+    if (nvec <= 32) return launch_cfg<OP, T, 32, 1>(p, stream);
+    if (nvec <= 64) return launch_cfg<OP, T, 32, 2>(p, stream);
+    if (nvec <= 128) return launch_cfg<OP, T, 32, 4>(p, stream);
+    if (nvec <= 256) return launch_cfg<OP, T, 32, 8>(p, stream);
+    if (nvec <= 512) return launch_cfg<OP, T, 32, 16>(p, stream);
+    if (nvec <= 1024) return launch_cfg<OP, T, 128, 8>(p, stream);
+    if (nvec <= 2048) return launch_cfg<OP, T, 256, 8>(p, stream);
+    if (nvec <= 4096) return launch_cfg<OP, T, 512, 8>(p, stream);
+    if (nvec <= 8192) return launch_cfg<OP, T, 1024, 8>(p, stream);
+    return launch_cfg<OP, T, 1024, 16>(p, stream);
+  }
+  const int64_t cap = static_cast<int64_t>(sm_count_of_current_device()) * 8;
+  const unsigned grid = static_cast<unsigned>(p.R < cap ? p.R : cap);
+  row_kernel_generic<OP, T><<<grid, 256, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? TRX_OK : TRX_ERR_CUDA;
+}
+
+template <int OP>
+static int launch_row_dtype(const RowParams& p, int x_dtype, cudaStream_t stream) {
+  switch (x_dtype) {
+    case TRX_F32: return launch_row<OP, float>(p, stream);
+    case TRX_F16: return launch_row<OP, __half>(p, stream);
+    case TRX_BF16: return launch_row<OP, __nv_bfloat16>(p, stream);
+    default: return TRX_ERR_DTYPE;
+  }
+}
+
+static bool dtype_ok(int d) { return d == TRX_F32 || d == TRX_F16 || d == TRX_BF16; }
+
+}  // namespace trx
+
+using namespace trx;
+
+extern "C" int trx_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd_or_null, int64_t R,
+                               int64_t C, int64_t x_row_stride, int64_t y_row_stride, float eps,
+                               int x_dtype, int w_dtype, void* stream) {
+  if (!dtype_ok(x_dtype) || !dtype_ok(w_dtype)) return TRX_ERR_DTYPE;
+  if (R < 0 || C <= 0) return TRX_ERR_SHAPE;
+  if (R == 0) return TRX_OK;
+  if (!x || !w || !y) return TRX_ERR_NULL_POINTER;
+  if (x_row_stride < C || y_row_stride < C) return TRX_ERR_STRIDE;
+  RowParams p{};
+  p.x = x; p.w = w; p.y = y; p.rstd = rstd_or_null;
+  p.R = R; p.C = C; p.x_stride = x_row_stride; p.y_stride = y_row_stride;
+  p.eps = eps; p.w_dtype = w_dtype;
+  return launch_row_dtype<OP_RMSNORM>(p, x_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int trx_layernorm_fwd(const void* x, const void* w_or_null, const void* b_or_null,
+                                 void* y, float* mean_or_null, float* rstd_or_null, int64_t R,
+                                 int64_t C, int64_t x_row_stride, int64_t y_row_stride, float eps,
+                                 int x_dtype, int wb_dtype, void* stream) {
+  if (!dtype_ok(x_dtype) || !dtype_ok(wb_dtype)) return TRX_ERR_DTYPE;
+  if (R < 0 || C <= 0) return TRX_ERR_SHAPE;
+  if (R == 0) return TRX_OK;
+  if (!x || !y) return TRX_ERR_NULL_POINTER;
+  if (x_row_stride < C || y_row_stride < C) return TRX_ERR_STRIDE;
+  RowParams p{};
+  p.x = x; p.w = w_or_null; p.b = b_or_null; p.y = y; p.mean = mean_or_null;
+  p.rstd = rstd_or_null;
+  p.R = R; p.C = C; p.x_stride = x_row_stride; p.y_stride = y_row_stride;
+  p.eps = eps; p.w_dtype = wb_dtype;
+  return launch_row_dtype<OP_LAYERNORM>(p, x_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int trx_quant_rowwise_i8(const void* x, int8_t* codes, float* scales, int64_t R,
+                                    int64_t C, int64_t x_row_stride, int64_t codes_row_stride,
+                                    int x_dtype, void* stream) {
+  if (!dtype_ok(x_dtype)) return TRX_ERR_DTYPE;
+  if (R < 0 || C <= 0) return TRX_ERR_SHAPE;
+  if (R == 0) return TRX_OK;
+  if (!x || !codes || !scales) return TRX_ERR_NULL_POINTER;
+  if (x_row_stride < C || codes_row_stride < C) return TRX_ERR_STRIDE;
+  RowParams p{};
+  p.x = x; p.codes = codes; p.scales = scales;
+  p.R = R; p.C = C; p.x_stride = x_row_stride; p.codes_stride = codes_row_stride;
+  return launch_row_dtype<OP_QUANT>(p, x_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int trx_rmsnorm_quant_i8(const void* x, const void* w, int8_t* codes, float* scales,
+                                    int64_t R, int64_t C, int64_t x_row_stride,
+                                    int64_t codes_row_stride, float eps, int x_dtype, int w_dtype,
+                                    void* stream) {
+  if (!dtype_ok(x_dtype) || !dtype_ok(w_dtype)) return TRX_ERR_DTYPE;
+  if (R < 0 || C <= 0) return TRX_ERR_SHAPE;
+  if (R == 0) return TRX_OK;
+  if (!x || !w || !codes || !scales) return TRX_ERR_NULL_POINTER;
+  if (x_row_stride < C || codes_row_stride < C) return TRX_ERR_STRIDE;
+  RowParams p{};
+  p.x = x; p.w = w; p.codes = codes; p.scales = scales;
+  p.R = R; p.C = C; p.x_stride = x_row_stride; p.codes_stride = codes_row_stride;
+  p.eps = eps; p.w_dtype = w_dtype;
+  return launch_row_dtype<OP_RMSNORM_QUANT>(p, x_dtype, static_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,322 @@
+"""Tensor-level entry points: torch tensors in, torch tensors out, C ABI in between.
+
+PyTorch is plumbing here (device memory, current stream, device guard); every
+computation is a kernel of libtrinix_b200.so. All functions require CUDA tensors and
+raise otherwise — there is no CPU path and no fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import I64x3
+
+_DTYPE_CODE = {torch.float32: _lib.TRX_F32, torch.float16: _lib.TRX_F16,
+               torch.bfloat16: _lib.TRX_BF16}
+
+GLU_ACTS = {"swiglu": _lib.GLU_SWIGLU, "geglu": _lib.GLU_GEGLU_TANH, "reglu": _lib.GLU_REGLU}
+
+# Number of kernels launched through this module (the benchmark reports it).
+launch_count = 0
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise TypeError(f"trinix_b200 supports float32/float16/bfloat16, got {t.dtype}") from None
+
+
+def _need_cuda(*ts: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError("trinix_b200 kernels require CUDA tensors (there is no CPU path)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"tensors on different devices: {dev} and {t.device}")
+    assert dev is not None
+    return dev
+
+
+def _stream(dev: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def _rows(x: torch.Tensor) -> torch.Tensor:
+    """View (or, if unavoidable, copy) x as 2-D (rows, C) with a unit column stride."""
+    c = x.shape[-1]
+    x2 = x.reshape(-1, c)
+    if x2.numel() and x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    return x2
+
+
+def _row_stride(x2: torch.Tensor) -> int:
+    return x2.stride(0) if x2.shape[0] > 1 else x2.shape[1]
+
+
+# ----------------------------------------------------------------------------- norms
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+            return_rstd: bool = False):
+    """RMSNorm over the last dim; output has x's dtype and shape."""
+    dev = _need_cuda(x, weight)
+    if weight.numel() != x.shape[-1]:
+        raise ValueError(f"weight has {weight.numel()} elements, rows have {x.shape[-1]}")
+    x2 = _rows(x)
+    w = weight.detach().contiguous()
+    y = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=dev)
+    rstd = torch.empty(x2.shape[0], dtype=torch.float32, device=dev) if return_rstd else None
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_rmsnorm_fwd(_ptr(x2), _ptr(w), _ptr(y), _ptr(rstd), x2.shape[0],
+                                         x2.shape[1], _row_stride(x2), x2.shape[1], float(eps),
+                                         _code(x2), _code(w), _stream(dev))
+    _lib.check("trx_rmsnorm_fwd", rc)
+    _count()
+    y = y.view(x.shape)
+    return (y, rstd) if return_rstd else y
+
+
+def layernorm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+              eps: float = 1e-5) -> torch.Tensor:
+    """LayerNorm over the last dim; weight/bias may be None."""
+    dev = _need_cuda(x, weight, bias)
+    x2 = _rows(x)
+    wb_dtype = weight.dtype if weight is not None else (bias.dtype if bias is not None else x.dtype)
+    w = weight.detach().contiguous() if weight is not None else None
+    b = bias.detach().to(wb_dtype).contiguous() if bias is not None else None
+    for t in (w, b):
+        if t is not None and t.numel() != x.shape[-1]:
+            raise ValueError("weight/bias size does not match the normalised dim")
+    y = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_layernorm_fwd(_ptr(x2), _ptr(w), _ptr(b), _ptr(y), None, None,
+                                           x2.shape[0], x2.shape[1], _row_stride(x2), x2.shape[1],
+                                           float(eps), _code(x2), _DTYPE_CODE[wb_dtype],
+                                           _stream(dev))
+    _lib.check("trx_layernorm_fwd", rc)
+    _count()
+    return y.view(x.shape)
+
+
+# ----------------------------------------------------------------------------- int8
+def quantize_rowwise(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per-row symmetric int8: returns (codes int8 of x's shape, scales fp32 of shape[:-1])."""
+    dev = _need_cuda(x)
+    x2 = _rows(x)
+    codes = torch.empty((x2.shape[0], x2.shape[1]), dtype=torch.int8, device=dev)
+    scales = torch.empty(x2.shape[0], dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_quant_rowwise_i8(_ptr(x2), _ptr(codes), _ptr(scales), x2.shape[0],
+                                              x2.shape[1], _row_stride(x2), x2.shape[1], _code(x2),
+                                              _stream(dev))
+    _lib.check("trx_quant_rowwise_i8", rc)
+    _count()
+    return codes.view(x.shape), scales.view(x.shape[:-1])
+
+
+def dequantize_rowwise(codes: torch.Tensor, scales: torch.Tensor,
+                       dtype: torch.dtype = torch.bfloat16,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Inverse of quantize_rowwise: round_dtype(float(code) * scale[row])."""
+    dev = _need_cuda(codes, scales)
+    if codes.dtype != torch.int8 or scales.dtype != torch.float32:
+        raise TypeError("codes must be int8 and scales float32")
+    c2 = _rows(codes)
+    s = scales.reshape(-1).contiguous()
+    if s.numel() != c2.shape[0]:
+        raise ValueError("one scale per row expected")
+    if out is None:
+        out = torch.empty((c2.shape[0], c2.shape[1]), dtype=dtype, device=dev)
+    elif out.dtype != dtype or out.numel() != c2.numel() or not out.is_contiguous():
+        raise ValueError("out must be a contiguous tensor of the requested dtype and size")
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_dequant_rowwise_i8(_ptr(c2), _ptr(s), _ptr(out), c2.shape[0],
+                                                c2.shape[1], _row_stride(c2), c2.shape[1],
+                                                _DTYPE_CODE[dtype], _stream(dev))
+    _lib.check("trx_dequant_rowwise_i8", rc)
+    _count()
+    return out.view(codes.shape)
+
+
+def rmsnorm_quantize(x: torch.Tensor, weight: torch.Tensor,
+                     eps: float = 1e-6) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Fused RMSNorm -> int8; equals quantize_rowwise(rmsnorm(x, weight, eps)) bit for bit."""
+    dev = _need_cuda(x, weight)
+    if weight.numel() != x.shape[-1]:
+        raise ValueError(f"weight has {weight.numel()} elements, rows have {x.shape[-1]}")
+    x2 = _rows(x)
+    w = weight.detach().contiguous()
+    codes = torch.empty((x2.shape[0], x2.shape[1]), dtype=torch.int8, device=dev)
+    scales = torch.empty(x2.shape[0], dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_rmsnorm_quant_i8(_ptr(x2), _ptr(w), _ptr(codes), _ptr(scales),
+                                              x2.shape[0], x2.shape[1], _row_stride(x2),
+                                              x2.shape[1], float(eps), _code(x2), _code(w),
+                                              _stream(dev))
+    _lib.check("trx_rmsnorm_quant_i8", rc)
+    _count()
+    return codes.view(x.shape), scales.view(x.shape[:-1])
+
+
+# ----------------------------------------------------------------------------- RoPE
+def _bshd(t: torch.Tensor) -> torch.Tensor:
+    if t.dim() != 4:
+        raise ValueError(f"expected (batch, seq, heads, head_dim), got {tuple(t.shape)}")
+    return t if t.stride(-1) == 1 or t.numel() == 0 else t.contiguous()
+
+
+def rope(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+         inverse: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Half-split rotary embedding of q (B,S,Hq,D) and k (B,S,Hk,D) in one launch.
+
+    cos/sin are (S, D) (or anything that squeezes to it); only columns < D/2 are read.
+    Tables must be float32 or have q's dtype.
+    """
+    dev = _need_cuda(q, k, cos, sin)
+    if q.dtype != k.dtype:
+        raise TypeError("q and k must share a dtype")
+    q, k = _bshd(q), _bshd(k)
+    B, S, Hq, D = q.shape
+    if k.shape[0] != B or k.shape[1] != S or k.shape[3] != D:
+        raise ValueError(f"k shape {tuple(k.shape)} does not match q {tuple(q.shape)}")
+    cos2 = cos.reshape(-1, cos.shape[-1])
+    sin2 = sin.reshape(-1, sin.shape[-1])
+    if cos2.shape != sin2.shape or cos2.shape[0] < S or cos2.shape[1] < D // 2:
+        raise ValueError("cos/sin tables must be (>= seq_len, >= head_dim/2) and alike")
+    if cos2.dtype != sin2.dtype or cos2.dtype not in (torch.float32, q.dtype):
+        cos2, sin2 = cos2.float(), sin2.float()
+    cos2, sin2 = cos2.contiguous(), sin2.contiguous()
+    qo = torch.empty((B, S, Hq, D), dtype=q.dtype, device=dev)
+    ko = torch.empty((B, S, k.shape[2], D), dtype=k.dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_rope_fwd(_ptr(q), _ptr(k), _ptr(cos2), _ptr(sin2), _ptr(qo), _ptr(ko),
+                                      B, S, Hq, k.shape[2], D, I64x3(*q.stride()[:3]),
+                                      I64x3(*k.stride()[:3]), I64x3(*qo.stride()[:3]),
+                                      I64x3(*ko.stride()[:3]), cos2.stride(0), _code(cos2),
+                                      _code(q), int(bool(inverse)), _stream(dev))
+    _lib.check("trx_rope_fwd", rc)
+    _count()
+    return qo, ko
+
+
+# ----------------------------------------------------------------------------- GLU
+def glu(x: torch.Tensor, act: str) -> torch.Tensor:
+    """x (..., 2H) -> (..., H): x[..., :H] * act(x[..., H:]); act in swiglu/geglu/reglu."""
+    dev = _need_cuda(x)
+    two_h = x.shape[-1]
+    if two_h % 2:
+        raise ValueError("last dimension must be even")
+    h = two_h // 2
+    x2 = _rows(x)
+    y = torch.empty((x2.shape[0], h), dtype=x.dtype, device=dev)
+    rs = _row_stride(x2)
+    up_ptr = x2.data_ptr()
+    gate_ptr = up_ptr + h * x2.element_size()
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_glu_fwd(ctypes.c_void_p(up_ptr), ctypes.c_void_p(gate_ptr), _ptr(y),
+                                     x2.shape[0], h, rs, rs, h, GLU_ACTS[act], _code(x2),
+                                     _stream(dev))
+    _lib.check("trx_glu_fwd", rc)
+    _count()
+    return y.view(*x.shape[:-1], h)
+
+
+def glu_pair(up: torch.Tensor, gate: torch.Tensor, act: str) -> torch.Tensor:
+    """Separate up / gate tensors of equal shape (..., H) -> up * act(gate)."""
+    dev = _need_cuda(up, gate)
+    if up.shape != gate.shape or up.dtype != gate.dtype:
+        raise ValueError("up and gate must have the same shape and dtype")
+    u2, g2 = _rows(up), _rows(gate)
+    y = torch.empty((u2.shape[0], u2.shape[1]), dtype=up.dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_glu_fwd(_ptr(u2), _ptr(g2), _ptr(y), u2.shape[0], u2.shape[1],
+                                     _row_stride(u2), _row_stride(g2), u2.shape[1], GLU_ACTS[act],
+                                     _code(u2), _stream(dev))
+    _lib.check("trx_glu_fwd", rc)
+    _count()
+    return y.view(up.shape)
+
+
+# ----------------------------------------------------------------------------- attention
+_workspaces: dict = {}
+
+
+def _workspace(dev: torch.device) -> torch.Tensor:
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None:
+        n = int(_lib.load().trx_attn_workspace_bytes())
+        ws = torch.zeros(n, dtype=torch.uint8, device=torch.device("cuda", idx))
+        _workspaces[idx] = ws
+    return ws
+
+
+def attention_status(device=None) -> int:
+    """Status word of the attention workspace on `device` (synchronises). Non-zero means a
+    bounded on-chip wait gave up in some earlier launch; the word is then cleared."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    ws = _workspace(dev)
+    word = int(ws[:4].view(torch.int32).item())
+    if word:
+        ws[:4].zero_()
+    return word
+
+
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = False,
+              scale: Optional[float] = None, window: Optional[Tuple[int, int]] = None,
+              alibi_slopes: Optional[torch.Tensor] = None, return_lse: bool = False):
+    """softmax(scale * q k^T + bias) v; q (B,Sq,Hq,D), k/v (B,Sk,Hk,D), Hq % Hk == 0.
+
+    Query head h reads kv head h // (Hq // Hk). window = (left, right) keeps keys with
+    -left <= j - i <= right. alibi_slopes (Hq,) adds -slope * |i - j|.
+    """
+    dev = _need_cuda(q, k, v, alibi_slopes)
+    if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("attention needs q, k, v of one dtype, bfloat16 or float16")
+    q, k, v = _bshd(q), _bshd(k), _bshd(v)
+    B, Sq, Hq, D = q.shape
+    Bk, Sk, Hk, Dk = k.shape
+    if (Bk, Dk) != (B, D) or v.shape != k.shape:
+        raise ValueError(f"k {tuple(k.shape)} / v {tuple(v.shape)} do not match q {tuple(q.shape)}")
+    if Hk == 0 or Hq % Hk:
+        raise ValueError(f"query heads ({Hq}) must be a multiple of kv heads ({Hk})")
+    if scale is None:
+        scale = D ** -0.5
+    wl, wr = (-1, -1)
+    if window is not None:
+        wl, wr = int(window[0]), int(window[1])
+        if wl < 0 or wr < 0:
+            raise ValueError("window sizes must be >= 0")
+    slopes = None
+    if alibi_slopes is not None:
+        slopes = alibi_slopes.detach().reshape(-1).to(torch.float32).contiguous()
+        if slopes.numel() != Hq:
+            raise ValueError(f"alibi_slopes must have {Hq} entries")
+    out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=dev)
+    lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=dev) if return_lse else None
+    ws = _workspace(dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse),
+                                      _ptr(slopes), B, Sq, Sk, Hq, Hk, D, I64x3(*q.stride()[:3]),
+                                      I64x3(*k.stride()[:3]), I64x3(*v.stride()[:3]),
+                                      I64x3(*out.stride()[:3]), float(scale), int(bool(causal)),
+                                      wl, wr, _code(q), _ptr(ws), ws.numel(), _stream(dev))
+    _lib.check("trx_attn_fwd", rc)
+    _count()
+    return (out, lse) if return_lse else out
