@@ -1,0 +1,161 @@
+"""Parity of the tcgen05 attention kernel with the CPU oracle (the reference's PyTorch
+attention), through triton_attn_func / the C ABI. Tolerance from the project baseline:
+2e-2 max abs error in bf16."""
+import pytest
+import torch
+
+import trinix_b200 as T
+from oracle import reference_port as R
+from tests.util import Golden
+
+pytestmark = pytest.mark.gpu
+G = Golden()
+TOL = 2e-2
+
+
+def _qkv(B, Sq, Sk, Hq, Hk, D, seed=0, dtype=torch.bfloat16):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, Sq, Hq, D, generator=g).to(dtype)
+    k = torch.randn(B, Sk, Hk, D, generator=g).to(dtype)
+    v = torch.randn(B, Sk, Hk, D, generator=g).to(dtype)
+    return q, k, v
+
+
+def _check(cuda, q, k, v, causal=False, window=None, slopes=None, scale=None, tol=TOL):
+    out = T.triton_attn_func(q.to(cuda), k.to(cuda), v.to(cuda), softmax_scale=scale,
+                             causal=causal, window_size=window,
+                             alibi_slopes=None if slopes is None else slopes.to(cuda))
+    assert T.attention_status(cuda) == 0, "a bounded wait inside the kernel gave up"
+    assert out.shape == q.shape and out.dtype == q.dtype
+    # the oracle in the kernel's input dtype (what the reference computes) and in fp32 (truth)
+    ref = R.attention_variant_ref(q, k, v, scale, causal, window, slopes).float()
+    ref32 = R.attention_variant_ref(q.float(), k.float(), v.float(), scale, causal, window,
+                                    None if slopes is None else slopes.float())
+    o = out.float().cpu()
+    assert not torch.isnan(o).any()
+    err, err32 = float((o - ref).abs().max()), float((o - ref32).abs().max())
+    assert err <= tol and err32 <= tol, (err, err32)
+    return out
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("S", [128, 256, 384, 1000])
+def test_noncausal_mha(cuda, S, D):
+    q, k, v = _qkv(1, S, S, 2, 2, D, seed=S + D)
+    _check(cuda, q, k, v)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("S", [64, 129, 512, 777, 1536])
+def test_causal_gqa(cuda, S, D):
+    q, k, v = _qkv(2, S, S, 8, 2, D, seed=S)
+    _check(cuda, q, k, v, causal=True)
+
+
+def test_causal_mqa_with_expanded_kv_heads(cuda):
+    """MQA as the reference's module presents it: one kv head expanded to all query heads
+    (head stride 0), multi_query_attention.py:173-174."""
+    q, k, v = _qkv(2, 300, 300, 4, 1, 128, seed=7)
+    ref = R.attention_variant_ref(q, k, v, None, True).float()
+    kd, vd = k.to("cuda").expand(-1, -1, 4, -1), v.to("cuda").expand(-1, -1, 4, -1)
+    assert kd.stride(2) == 0
+    out = T.triton_attn_func(q.to("cuda"), kd, vd, causal=True)
+    assert T.attention_status() == 0
+    assert float((out.float().cpu() - ref).abs().max()) <= TOL
+    out1 = T.triton_attn_func(q.to("cuda"), k.to("cuda"), v.to("cuda"), causal=True)
+    assert torch.equal(out, out1)  # native Hkv=1 and the expanded view are the same launch
+
+
+def test_tiled_noncontiguous_kv_like_the_reference_module(cuda):
+    """K/V tiled to all heads and handed over as transposed (B,S,H,D) views, the layout
+    grouped_query_attention.py:189-194 produces."""
+    q, k, v = _qkv(2, 260, 260, 8, 2, 128, seed=11)
+    kt = R.tile_kv_heads_ref(k, 4).to("cuda").transpose(1, 2).contiguous().transpose(1, 2)
+    vt = R.tile_kv_heads_ref(v, 4).to("cuda").transpose(1, 2).contiguous().transpose(1, 2)
+    assert not kt.is_contiguous()
+    out = T.triton_attn_func(q.to("cuda"), kt, vt, causal=True)
+    native = T.triton_attn_func(q.to("cuda"), k.to("cuda"), v.to("cuda"), causal=True)
+    assert T.attention_status() == 0
+    assert torch.equal(out, native)
+
+
+@pytest.mark.parametrize("S", [200, 1024])
+def test_causal_alibi(cuda, S):
+    H = 8
+    q, k, v = _qkv(1, S, S, H, 2, 128, seed=S)
+    slopes = R.alibi_slopes_ref(H)
+    _check(cuda, q, k, v, causal=True, slopes=slopes)
+    _check(cuda, q, k, v, causal=False, slopes=slopes)  # |i-j| on both sides
+
+
+@pytest.mark.parametrize("S,window", [(700, (100, 0)), (1300, (256, 0)), (600, (64, 64)),
+                                      (512, (0, 0)), (900, (1024, 0)), (520, (130, 7))])
+def test_sliding_window(cuda, S, window):
+    q, k, v = _qkv(1, S, S, 4, 2, 128, seed=S)
+    _check(cuda, q, k, v, window=window)
+    _check(cuda, q, k, v, causal=True, window=(window[0], max(window)))
+
+
+def test_window_zero_zero_returns_v(cuda):
+    q, k, v = _qkv(1, 300, 300, 2, 2, 64, seed=1)
+    out = T.triton_attn_func(q.to(cuda), k.to(cuda), v.to(cuda), window_size=(0, 0))
+    assert torch.equal(out.cpu(), v)  # softmax over a single key is exactly 1
+
+
+def test_cross_lengths_scale_and_fp16(cuda):
+    q, k, v = _qkv(2, 200, 333, 4, 4, 128, seed=3)
+    _check(cuda, q, k, v, scale=0.05)
+    q, k, v = _qkv(1, 130, 70, 2, 1, 64, seed=4, dtype=torch.float16)
+    _check(cuda, q, k, v, tol=5e-3)
+    q, k, v = _qkv(1, 260, 130, 2, 1, 128, seed=5)
+    _check(cuda, q, k, v, causal=True)  # rows beyond the key count see every key
+
+
+def test_large_logits_trigger_rescale(cuda):
+    """Row maxima that keep growing along the keys force the O-rescale path."""
+    g = torch.Generator().manual_seed(0)
+    S, D = 1024, 128
+    q = torch.randn(1, S, 1, D, generator=g)
+    k = torch.randn(1, S, 1, D, generator=g) * torch.linspace(0.2, 3.0, S).view(1, S, 1, 1)
+    v = torch.randn(1, S, 1, D, generator=g)
+    _check(cuda, q.bfloat16(), k.bfloat16(), v.bfloat16(), scale=0.5, tol=3e-2)
+
+
+def test_lse_output(cuda):
+    q, k, v = _qkv(1, 300, 300, 2, 2, 128, seed=2)
+    out, lse = T.attention(q.to(cuda), k.to(cuda), v.to(cuda), causal=True, return_lse=True)
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), k.float()) * 128 ** -0.5
+    s = s.masked_fill(torch.triu(torch.ones(300, 300), 1).bool(), float("-inf"))
+    torch.testing.assert_close(lse.cpu(), torch.logsumexp(s, -1), rtol=1e-3, atol=1e-3)
+
+
+def test_golden_core_vectors_d32_rejected_cleanly(cuda):
+    """head_dim 32 (the golden attention vectors) is outside this build: a clear error, no
+    fallback."""
+    q = G("attn_q").bfloat16().to(cuda)
+    with pytest.raises(T._lib.TrinixB200Error) as e:
+        T.triton_attn_func(q, q, q)
+    assert e.value.code == -6
+
+
+def test_full_size_properties(cuda):
+    """Benchmark geometry (S=4096, 32 query / 8 kv heads, D=128), one batch element:
+    causal output row 0 equals v[0]; batch sharding is bit-identical; window (S, 0) == causal."""
+    g = torch.Generator(device=cuda).manual_seed(0)
+    B, S, H, Hk, D = 2, 4096, 32, 8, 128
+    q = torch.randn(B, S, H, D, generator=g, device=cuda).bfloat16()
+    k = torch.randn(B, S, Hk, D, generator=g, device=cuda).bfloat16()
+    v = torch.randn(B, S, Hk, D, generator=g, device=cuda).bfloat16()
+    out = T.triton_attn_func(q, k, v, causal=True)
+    assert T.attention_status(cuda) == 0
+    assert torch.equal(out[:, 0], v[:, 0].repeat_interleave(4, dim=1))
+    parts = torch.cat([T.triton_attn_func(q[b:b + 1], k[b:b + 1], v[b:b + 1], causal=True)
+                       for b in range(B)])
+    assert torch.equal(out, parts)
+    w = T.triton_attn_func(q, k, v, window_size=(S, 0))
+    assert torch.equal(out, w)
+    # against torch's own fused attention on the GPU (a library used as checker only)
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        q.transpose(1, 2), k.transpose(1, 2).repeat_interleave(4, 1),
+        v.transpose(1, 2).repeat_interleave(4, 1), is_causal=True).transpose(1, 2)
+    assert float((out.float() - ref.float()).abs().max()) <= TOL

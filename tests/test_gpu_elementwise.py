@@ -1,0 +1,100 @@
+"""Parity of the streaming kernels (GLUs, RoPE) with the CPU oracle, through the C ABI."""
+import pytest
+import torch
+
+import trinix_b200 as T
+from oracle import reference_port as R
+from tests.util import Golden, bf16_ulps, rel_err
+
+pytestmark = pytest.mark.gpu
+G = Golden()
+GLU = {"swiglu": (T.TritonSwiGLUKernel, R.swiglu_ref), "geglu": (T.TritonGeGLUKernel, R.geglu_ref),
+       "reglu": (T.TritonReGLUKernel, R.reglu_ref)}
+
+
+@pytest.mark.parametrize("name", list(GLU))
+def test_glu_golden(cuda, name):
+    kern, _ = GLU[name]
+    y = kern.apply(G(f"{name}_f32_x").to(cuda)).cpu()
+    torch.testing.assert_close(y, G(f"{name}_f32_y"), rtol=2e-5, atol=2e-6)
+    yb = kern.apply(G(f"{name}_x").to(cuda)).cpu()
+    assert rel_err(yb, G(f"{name}_y")) <= 1e-2
+
+
+@pytest.mark.parametrize("name", list(GLU))
+@pytest.mark.parametrize("shape", [(1, 16), (3, 2 * 100), (2, 5, 2 * 11008), (7, 2 * 1021),
+                                   (1030, 2 * 512)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_glu_shapes(cuda, name, shape, dtype):
+    kern, ref = GLU[name]
+    g = torch.Generator().manual_seed(len(shape) + shape[-1])
+    x = (torch.randn(*shape, generator=g) * 3).to(dtype)
+    x.view(-1)[:4] = torch.tensor([-100.0, 100.0, 0.0, -20.0]).to(dtype)  # saturation, no NaN
+    y = kern.apply(x.to(cuda)).cpu()
+    r = ref(x)
+    assert y.shape == r.shape and y.dtype == dtype
+    assert not torch.isnan(y.float()).any()
+    assert rel_err(y, r) <= (2e-5 if dtype == torch.float32 else 1e-2)
+    if dtype == torch.bfloat16:
+        d = bf16_ulps(y, r)
+        assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 5e-3
+
+
+def test_glu_separate_pointers_match_concatenated(cuda):
+    g = torch.Generator().manual_seed(0)
+    gate = torch.randn(4, 64, 11008, generator=g).bfloat16().to(cuda)
+    up = torch.randn(4, 64, 11008, generator=g).bfloat16().to(cuda)
+    a = T.glu_pair(up, gate, "swiglu")
+    b = T.glu(torch.cat([up, gate], dim=-1), "swiglu")  # gate is the SECOND half
+    assert torch.equal(a, b)
+    ref = R.swiglu_ref(torch.cat([up, gate], dim=-1).cpu())
+    assert rel_err(a.cpu(), ref) <= 1e-2
+
+
+def test_rope_golden_bit_exact(cuda):
+    q, k = G("rope_q").to(cuda), G("rope_k").to(cuda)
+    # fp32 tables: the oracle's result is fp32 (type promotion); the kernel rounds it once
+    qo, ko = T.TritonRoPEKernel.apply(q, k, G("rope_cos_f32").to(cuda), G("rope_sin_f32").to(cuda))
+    assert torch.equal(qo.cpu(), G("rope_qo_f32tab").bfloat16())
+    assert torch.equal(ko.cpu(), G("rope_ko_f32tab").bfloat16())
+    # tables in the activation dtype (what the reference's attention modules pass)
+    qo, ko = T.TritonRoPEKernel.apply(q, k, G("rope_cos").to(cuda), G("rope_sin").to(cuda))
+    assert torch.equal(qo.cpu(), G("rope_qo")) and torch.equal(ko.cpu(), G("rope_ko"))
+
+
+@pytest.mark.parametrize("B,S,Hq,Hk,D", [(2, 600, 32, 8, 128), (1, 7, 3, 1, 64), (2, 33, 5, 5, 32),
+                                         (1, 5, 2, 2, 6), (1, 2048, 4, 1, 128)])
+@pytest.mark.parametrize("dtype,table", [(torch.bfloat16, torch.float32),
+                                         (torch.bfloat16, torch.bfloat16),
+                                         (torch.float16, torch.float16),
+                                         (torch.float32, torch.float32)])
+def test_rope_shapes(cuda, B, S, Hq, Hk, D, dtype, table):
+    g = torch.Generator().manual_seed(S + D)
+    q = torch.randn(B, S, Hq, D, generator=g).to(dtype)
+    k = torch.randn(B, S, Hk, D, generator=g).to(dtype)
+    cos, sin = R.rope_tables_ref(D, S, 10000.0, table)
+    rq, rk = R.rope_ref(q, k, cos, sin)
+    qo, ko = T.rope(q.to(cuda), k.to(cuda), cos.to(cuda), sin.to(cuda))
+    assert qo.dtype == dtype and qo.shape == q.shape and ko.shape == k.shape
+    if dtype == torch.float32:
+        assert torch.equal(qo.cpu(), rq) and torch.equal(ko.cpu(), rk)
+    else:
+        assert torch.equal(qo.cpu(), rq.to(dtype)) and torch.equal(ko.cpu(), rk.to(dtype))
+    # inverse rotation restores the input up to rounding
+    if table == torch.float32:
+        qb, kb = T.rope(qo, ko, cos.to(cuda), sin.to(cuda), inverse=True)
+        assert rel_err(qb.cpu(), q) <= (1e-5 if dtype == torch.float32 else 2e-2)
+
+
+def test_rope_strided_views_from_fused_qkv(cuda):
+    """q/k taken as views of one fused projection output (non-contiguous head stride)."""
+    g = torch.Generator().manual_seed(1)
+    B, S, H, D = 2, 520, 8, 128
+    qkv = torch.randn(B, S, 3, H, D, generator=g).bfloat16()
+    q, k, _ = qkv.unbind(2)
+    cos, sin = R.rope_tables_ref(D, S, 10000.0, torch.float32)
+    rq, rk = R.rope_ref(q, k, cos, sin)
+    dq, dk, _ = qkv.to(cuda).unbind(2)
+    assert not dq.is_contiguous()
+    qo, ko = T.rope(dq, dk, cos.to(cuda), sin.to(cuda))
+    assert torch.equal(qo.cpu(), rq.bfloat16()) and torch.equal(ko.cpu(), rk.bfloat16())

@@ -1,0 +1,176 @@
+"""Parity of the row kernels (RMSNorm, LayerNorm, int8 quantise / dequantise, fused
+RMSNorm->int8) with the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import trinix_b200 as T
+from oracle import int8_numpy as N, reference_port as R
+from tests.util import Golden, bf16_ulps, outlier_matrix, rel_err
+
+pytestmark = pytest.mark.gpu
+G = Golden()
+
+
+def test_rmsnorm_fp32_baseline_config_golden(cuda):
+    """FastRMSNorm(768, eps=1e-6) fp32 on the reference's own output vector."""
+    y = T.TritonRMSNormKernel.apply(G("rms_f32_x").to(cuda), G("rms_f32_w").to(cuda), 1e-6)
+    torch.testing.assert_close(y.cpu(), G("rms_f32_y"), rtol=1e-5, atol=1e-6)
+
+
+def test_rmsnorm_fp32_full_config(cuda):
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(4, 128, 768, generator=g)
+    w = 1 + 0.02 * torch.randn(768, generator=g)
+    y, rstd = T.ops.rmsnorm(x.to(cuda), w.to(cuda), 1e-6, return_rstd=True)
+    ref = R.rmsnorm_ref(x, w, 1e-6)
+    torch.testing.assert_close(y.cpu(), ref, rtol=1e-5, atol=1e-6)
+    ref_rstd = torch.rsqrt(x.pow(2).mean(-1) + 1e-6).flatten()
+    torch.testing.assert_close(rstd.cpu(), ref_rstd, rtol=1e-6, atol=0)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 8), (3, 72), (5, 256), (7, 1000), (4, 2048),
+                                       (64, 4096), (3, 4104), (2, 8192), (2, 16384), (2, 32768),
+                                       (1, 65536 + 8), (2, 131080), (3, 777)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_rmsnorm_shapes(cuda, rows, cols, dtype):
+    g = torch.Generator().manual_seed(rows * 131 + cols)
+    x = torch.randn(rows, cols, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype)
+    y = T.ops.rmsnorm(x.to(cuda), w.to(cuda), 1e-6).cpu()
+    ref = R.rmsnorm_ref(x, w, 1e-6)
+    assert y.dtype == dtype and y.shape == x.shape
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert rel_err(y, ref) <= tol
+    if dtype == torch.bfloat16:
+        # same rounding order as the oracle: at most 1 ulp apart, and almost everywhere equal
+        d = bf16_ulps(y, ref)
+        assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 2e-3
+
+
+def test_rmsnorm_mixed_weight_dtype_and_strided_rows(cuda):
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(16, 2, 4096, generator=g).bfloat16()
+    w32 = 1 + 0.02 * torch.randn(4096, generator=g)
+    xs = x.to(cuda)[:, 0, :]  # row stride 8192
+    y = T.ops.rmsnorm(xs, w32.to(cuda), 1e-6).cpu()
+    ref = R.rmsnorm_ref(x[:, 0, :], w32, 1e-6)  # fp32 (promotion); kernel returns bf16 of it
+    assert y.dtype == torch.bfloat16
+    assert int(bf16_ulps(y, ref.bfloat16()).max()) <= 1
+    # unaligned base pointer -> scalar path, same numbers
+    flat = torch.randn(4 * 520 + 1, generator=g).bfloat16()
+    xu = flat[1:].view(4, 520)
+    yu = T.ops.rmsnorm(flat.to(cuda)[1:].view(4, 520), torch.ones(520, device=cuda), 1e-6).cpu()
+    assert rel_err(yu, R.rmsnorm_ref(xu, torch.ones(520), 1e-6)) <= 1e-2
+
+
+def test_layernorm_golden_and_shapes(cuda):
+    y = T.TritonLayerNormKernel.apply(G("ln_f32_x").to(cuda), G("ln_f32_w").to(cuda),
+                                      G("ln_f32_b").to(cuda), 1e-5)
+    torch.testing.assert_close(y.cpu(), G("ln_f32_y"), rtol=1e-5, atol=2e-6)
+    yb = T.TritonLayerNormKernel.apply(G("ln_bf16_x").to(cuda), None, None, 1e-5)
+    assert rel_err(yb.cpu(), G("ln_bf16_y")) <= 1e-2
+    g = torch.Generator().manual_seed(4)
+    for rows, cols, dtype in [(5, 8192, torch.bfloat16), (3, 4104, torch.float32),
+                              (2, 1001, torch.float16), (9, 12288, torch.bfloat16)]:
+        x = (torch.randn(rows, cols, generator=g) * 2 + 0.5).to(dtype)
+        w = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype)
+        b = (0.1 * torch.randn(cols, generator=g)).to(dtype)
+        y = T.ops.layernorm(x.to(cuda), w.to(cuda), b.to(cuda), 1e-5).cpu()
+        assert rel_err(y, R.layernorm_ref(x, w, b, 1e-5)) <= (1e-4 if dtype == torch.float32 else 1e-2)
+        y = T.ops.layernorm(x.to(cuda), w.to(cuda), None, 1e-5).cpu()
+        assert rel_err(y, R.layernorm_ref(x, w, None, 1e-5)) <= (1e-4 if dtype == torch.float32 else 1e-2)
+
+
+def _assert_quant_exact(x_cpu, codes, scales):
+    rc, rs = R.quantize_rowwise_ref(x_cpu)
+    assert torch.equal(scales.cpu().view(torch.int32), rs.view(torch.int32)), "scales differ"
+    assert torch.equal(codes.cpu(), rc), "codes differ"
+
+
+def test_quantize_benchmark_config_bit_exact(cuda):
+    """bf16 [8192, 4096] ~ N(0,1) with 0.1% outliers x20: codes and scales bit-exact."""
+    x = outlier_matrix(8192, 4096, seed=0).bfloat16()
+    codes, scales = T.quantize_rowwise(x.to(cuda))
+    assert codes.dtype == torch.int8 and scales.dtype == torch.float32
+    _assert_quant_exact(x, codes, scales)
+    # numpy restatement too
+    bits = x.view(torch.int16).numpy().view(np.uint16)
+    cn, sn = N.quantize_rowwise_np(N.bf16_bits_to_f32(bits[:512]))
+    assert np.array_equal(codes[:512].cpu().numpy(), cn)
+    deq = T.dequantize_rowwise(codes, scales, torch.bfloat16)
+    ref = R.dequantize_rowwise_ref(codes.cpu(), scales.cpu(), torch.bfloat16)
+    assert torch.equal(deq.cpu().view(torch.int16), ref.view(torch.int16))
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 8), (4, 16), (3, 100), (5, 1000), (2, 4104),
+                                       (3, 16384), (2, 40000), (1, 200000), (6, 11008)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_quantize_edge_cases_bit_exact(cuda, rows, cols, dtype):
+    g = torch.Generator().manual_seed(cols)
+    x = (torch.randn(rows, cols, generator=g) * 3).to(dtype)
+    if rows > 1:
+        x[1] = 0  # zero row -> scale 0, codes 0
+    x[0, 0] = 127.0  # forces exact ties x.5 for small integers + 0.5
+    if cols > 4:
+        x[0, 1:5] = torch.tensor([0.5, 1.5, -2.5, 63.5]).to(dtype)
+        x[0] = x[0].clamp(-127, 127)
+    codes, scales = T.quantize_rowwise(x.to(cuda))
+    _assert_quant_exact(x, codes, scales)
+    for out_dtype in (torch.bfloat16, torch.float32):
+        deq = T.dequantize_rowwise(codes, scales, out_dtype).cpu()
+        ref = R.dequantize_rowwise_ref(codes.cpu(), scales.cpu(), out_dtype)
+        assert torch.equal(deq.view(torch.int16 if out_dtype == torch.bfloat16 else torch.int32),
+                           ref.view(torch.int16 if out_dtype == torch.bfloat16 else torch.int32))
+
+
+def test_quantize_extreme_scales_bit_exact(cuda):
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(6, 512, generator=g)
+    x[0] *= 1e-30; x[1] *= 1e30; x[2] *= 1e-38; x[3] *= 3e37
+    for dtype in (torch.float32, torch.bfloat16):
+        xd = x.to(dtype)
+        codes, scales = T.quantize_rowwise(xd.to(cuda))
+        _assert_quant_exact(xd, codes, scales)
+
+
+def test_fused_rmsnorm_quant_equals_unfused_bit_exact(cuda):
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(4, 512, 4096, generator=g).bfloat16()
+    w = (1 + 0.02 * torch.randn(4096, generator=g)).bfloat16()
+    xd, wd = x.to(cuda), w.to(cuda)
+    codes, scales = T.rmsnorm_quantize(xd, wd, 1e-6)
+    y = T.ops.rmsnorm(xd, wd, 1e-6)
+    c2, s2 = T.quantize_rowwise(y)
+    assert torch.equal(codes, c2) and torch.equal(scales.view(torch.int32), s2.view(torch.int32))
+    # given the kernel's bf16 norm output, the oracle's quantiser reproduces codes and scales
+    _assert_quant_exact(y.cpu(), codes, scales)
+    # against the full CPU oracle only the fp32 reduction order of mean(x^2) differs
+    rc, rs = R.rmsnorm_quantize_ref(x, w, 1e-6)
+    dc = (codes.cpu().int() - rc.int()).abs()
+    assert int(dc.max()) <= 1 and float((dc > 0).float().mean()) < 5e-3
+    torch.testing.assert_close(scales.cpu(), rs, rtol=1e-2, atol=0)
+    for rows, cols, dtype in [(3, 520, torch.bfloat16), (5, 777, torch.float16),
+                              (2, 8192, torch.float32), (2, 70000, torch.bfloat16)]:
+        xx = torch.randn(rows, cols, generator=g).to(dtype).to(cuda)
+        ww = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype).to(cuda)
+        c, s = T.rmsnorm_quantize(xx, ww, 1e-6)
+        c2, s2 = T.quantize_rowwise(T.ops.rmsnorm(xx, ww, 1e-6))
+        assert torch.equal(c, c2) and torch.equal(s.view(torch.int32), s2.view(torch.int32))
+
+
+def test_quantize_full_size_properties(cuda):
+    """Size-independent properties at the benchmark's full size ([16,2048,4096] activations)."""
+    g = torch.Generator(device=cuda).manual_seed(0)
+    x = torch.randn(16, 2048, 4096, generator=g, device=cuda, dtype=torch.float32).bfloat16()
+    w = torch.ones(4096, device=cuda, dtype=torch.bfloat16)
+    codes, scales = T.rmsnorm_quantize(x, w, 1e-6)
+    assert codes.shape == x.shape and scales.shape == x.shape[:-1]
+    assert int(codes.abs().amax(-1).min()) == 127  # every row hits +-127 exactly once at least
+    y = T.ops.rmsnorm(x, w, 1e-6)
+    deq = T.dequantize_rowwise(codes, scales, torch.float32)
+    assert bool(((deq - y.float()).abs() <= 0.5005 * scales.unsqueeze(-1)).all())
+    # idempotence: re-quantising the dequantised codes (exact in fp32) returns the same codes
+    c2, s2 = T.quantize_rowwise(deq)
+    assert torch.equal(c2, codes)
+    assert torch.equal(T.quantize_rowwise(y)[0], codes)
