@@ -34,7 +34,11 @@ def _check(cuda, q, k, v, causal=False, window=None, slopes=None, scale=None, to
     o = out.float().cpu()
     assert not torch.isnan(o).any()
     err, err32 = float((o - ref).abs().max()), float((o - ref32).abs().max())
-    assert err <= tol and err32 <= tol, (err, err32)
+    # The 16-bit oracle rounds scores and probabilities to the input dtype (base.py:373,394),
+    # so it sits up to `oracle_noise` away from the exact result itself; the kernel must be
+    # within tol of the exact result and within tol + that noise of the 16-bit oracle.
+    oracle_noise = float((ref - ref32).abs().max())
+    assert err32 <= tol and err <= tol + oracle_noise, (err, err32, oracle_noise)
     return out
 
 

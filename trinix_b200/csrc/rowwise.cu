@@ -5,15 +5,34 @@
 // thread, TPR threads per row); statistics are reduced with warp shuffles
 // (plus one shared-memory hop when a row spans more than one warp), and the
 // result is produced from the registers — the row is never re-read.
-//   TPR == 32 : one warp per row, 8 rows per 256-thread CTA, no barriers at all.
-//   TPR  > 32 : one CTA per row.
+//   TPR == 32 : one warp per row, 8 rows per 256-thread CTA, no barriers at all (short rows).
+//   TPR  > 32 : one CTA of TPR threads per row, few vectors per thread.
 // CTAs are persistent: the grid is sized to what the 148 SMs can hold and
 // strides over the rows. Rows that do not fit the vector path (columns not a
 // multiple of the vector width, unaligned pointers, more than 16384 vectors)
 // take a scalar multi-pass kernel, so nothing is ever truncated.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace trx {
+
+// (threads per row, vectors per thread) for rows of up to 256 / 512 vectors (4096 bf16
+// columns sit in the second class). Few vectors per thread keep register pressure low enough
+// for 10+ CTAs per SM; the row then spans several warps and pays one barrier per reduction.
+#ifndef TRX_ROW256_TPR
+#define TRX_ROW256_TPR 64
+#define TRX_ROW256_VPT 4
+#endif
+#ifndef TRX_ROW512_TPR
+#define TRX_ROW512_TPR 128
+#define TRX_ROW512_VPT 4
+#endif
+
+// Minimum resident CTAs per SM asked of the compiler (caps registers per thread).
+#ifndef TRX_ROW_MINBLOCKS
+#define TRX_ROW_MINBLOCKS(TPR) ((TPR) > 32 ? ((TPR) <= 256 ? 1024 / (TPR) : 1) : 3)
+#endif
 
 enum RowOp { OP_RMSNORM = 0, OP_LAYERNORM = 1, OP_QUANT = 2, OP_RMSNORM_QUANT = 3 };
 
@@ -55,7 +74,7 @@ __device__ __forceinline__ uint32_t mul_packed16<float>(uint32_t a, uint32_t) {
 }
 
 template <int OP, typename T, int TPR, int VPT>
-__global__ void __launch_bounds__((TPR > 32 ? TPR : 256))
+__global__ void __launch_bounds__((TPR > 32 ? TPR : 256), TRX_ROW_MINBLOCKS(TPR))
     row_kernel(const RowParams p) {
   using P = Pack<T>;
   constexpr int VEC = P::VEC;
@@ -64,28 +83,36 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256))
   constexpr bool HAS_NORM = (OP == OP_RMSNORM || OP == OP_LAYERNORM || OP == OP_RMSNORM_QUANT);
   constexpr bool HAS_QUANT = (OP == OP_QUANT || OP == OP_RMSNORM_QUANT);
 
-  __shared__ float red[2][32];
+  __shared__ __align__(16) float red[2][32];
   int sel = 0;
 
   const int t = threadIdx.x % TPR;
   const int row_in_cta = threadIdx.x / TPR;
   const int nvec = static_cast<int>(p.C / VEC);
 
+  const int64_t row_step = static_cast<int64_t>(gridDim.x) * ROWS_PER_CTA;
+  // fp32 copies of the row are kept between the statistics and the normalise pass when they
+  // fit (saves re-unpacking); longer per-thread slices unpack twice instead.
+  constexpr bool KEEP_F32 = (VEC == 8) && (VPT <= 4) && (OP == OP_RMSNORM || OP == OP_RMSNORM_QUANT);
+
   for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * ROWS_PER_CTA; row0 < p.R;
-       row0 += static_cast<int64_t>(gridDim.x) * ROWS_PER_CTA) {
+       row0 += row_step) {
     const int64_t row = row0 + row_in_cta;
     const bool row_ok = row < p.R;
-    if (TPR == 32 && !row_ok) continue;  // warp-uniform; no barriers on this path
 
-    // ---- 1. the one and only HBM read of the row --------------------------------
+    // ---- 1. the one and only HBM read of the row ------------------------------------
     uint4 raw[VPT];
-    const T* xrow = reinterpret_cast<const T*>(p.x) + (row_ok ? row : 0) * p.x_stride;
+    {
+      const T* xrow = reinterpret_cast<const T*>(p.x) + (row_ok ? row : 0) * p.x_stride;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int v = i * TPR + t;
-      raw[i] = (row_ok && v < nvec) ? ld_stream16(xrow + static_cast<int64_t>(v) * VEC)
-                                    : make_uint4(0u, 0u, 0u, 0u);
+      for (int i = 0; i < VPT; ++i) {
+        const int v = i * TPR + t;
+        raw[i] = (row_ok && v < nvec) ? ld_stream16(xrow + static_cast<int64_t>(v) * VEC)
+                                      : make_uint4(0u, 0u, 0u, 0u);
+      }
     }
+    float2 xf[KEEP_F32 ? VPT : 1][VEC / 2];
+    (void)xf;
 
     float mean = 0.0f, rstd = 1.0f;
     // ---- 2. statistics -------------------------------------------------------------
@@ -96,7 +123,10 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256))
         float2 f2[VEC / 2];
         P::unpack2(raw[i], f2);
 #pragma unroll
-        for (int j = 0; j < VEC / 2; ++j) ss2 = fma2(f2[j], f2[j], ss2);
+        for (int j = 0; j < VEC / 2; ++j) {
+          ss2 = fma2(f2[j], f2[j], ss2);
+          if constexpr (KEEP_F32) xf[i][j] = f2[j];
+        }
       }
       float ss = row_reduce<TPR, false>(ss2.x + ss2.y, red, sel);
       const float var = __fdiv_rn(ss, static_cast<float>(p.C));
@@ -138,18 +168,26 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256))
     }
 
     // ---- 3. normalise (registers -> registers, or registers -> HBM) ----------------
+    // All dtype / null-pointer decisions are taken once per row, outside the vector loops.
     if constexpr (HAS_NORM) {
       T* yrow = (OP == OP_RMSNORM_QUANT)
                     ? nullptr
                     : reinterpret_cast<T*>(p.y) + (row_ok ? row : 0) * p.y_stride;
+      auto emit = [&](int i, int64_t col, const uint4& packed) {
+        if constexpr (OP == OP_RMSNORM_QUANT) {
+          raw[i] = packed;
+        } else {
+          st_stream16(yrow + col, packed);
+        }
+      };
+      if constexpr (OP == OP_LAYERNORM) {
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = i * TPR + t;
-        if (row_ok && v < nvec) {
-          float f[VEC];
-          P::unpack(raw[i], f);
-          const int64_t col = static_cast<int64_t>(v) * VEC;
-          if constexpr (OP == OP_LAYERNORM) {
+        for (int i = 0; i < VPT; ++i) {
+          const int v = i * TPR + t;
+          if (row_ok && v < nvec) {
+            float f[VEC];
+            P::unpack(raw[i], f);
+            const int64_t col = static_cast<int64_t>(v) * VEC;
             float wv[VEC], bv[VEC];
             if (p.w) load_param_vec<VEC>(p.w, p.w_dtype, col, wv);
             if (p.b) load_param_vec<VEC>(p.b, p.w_dtype, col, bv);
@@ -160,43 +198,60 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256))
               if (p.b) o += bv[j];
               f[j] = o;
             }
-          } else {
-            // round(x * rstd) to the activation dtype, then times w, then round again:
-            // the order of the reference's PyTorch backend.
-            if constexpr (VEC == 8) {
-              if (p.w_dtype == P::DTYPE) {
-                // Same 16-bit dtype on both sides: the second product is a single packed
-                // multiply with one rounding (the exact product fits in fp32).
+            emit(i, col, P::pack(f));
+          }
+        }
+      } else {
+        // round(x * rstd) to the activation dtype, then times w, then round again: the order
+        // of the reference's PyTorch backend.
+        bool done = false;
+        if constexpr (VEC == 8) {
+          if (p.w_dtype == P::DTYPE) {
+            // Same 16-bit dtype on both sides: x*rstd as a packed fp32x2 multiply, one packed
+            // convert, and the second product as one packed 16-bit multiply (single rounding:
+            // the exact product of two 16-bit values fits in fp32).
+            done = true;
+            const float2 r2 = make_float2(rstd, rstd);
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+              const int v = i * TPR + t;
+              if (row_ok && v < nvec) {
+                const int64_t col = static_cast<int64_t>(v) * VEC;
                 const uint4 wraw = ld_cached16(reinterpret_cast<const T*>(p.w) + col);
                 const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wraw);
+                float2 f2[4];
+                if constexpr (KEEP_F32) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) f2[j] = xf[i][j];
+                } else {
+                  P::unpack2(raw[i], f2);
+                }
                 uint32_t yu[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                  const uint32_t n2 =
-                      P::pack2(__fmul_rn(f[2 * j], rstd), __fmul_rn(f[2 * j + 1], rstd));
-                  yu[j] = mul_packed16<T>(wu[j], n2);
+                  const float2 n = mul2(f2[j], r2);
+                  yu[j] = mul_packed16<T>(wu[j], P::pack2(n.x, n.y));
                 }
-                const uint4 packed16 = make_uint4(yu[0], yu[1], yu[2], yu[3]);
-                if constexpr (OP == OP_RMSNORM_QUANT) {
-                  raw[i] = packed16;
-                } else {
-                  st_stream16(yrow + col, packed16);
-                }
-                continue;
+                emit(i, col, make_uint4(yu[0], yu[1], yu[2], yu[3]));
               }
             }
-            float wv[VEC];
-            load_param_vec<VEC>(p.w, p.w_dtype, col, wv);
-#pragma unroll
-            for (int j = 0; j < VEC; ++j) {
-              f[j] = __fmul_rn(wv[j], P::round(__fmul_rn(f[j], rstd)));
-            }
           }
-          const uint4 packed = P::pack(f);
-          if constexpr (OP == OP_RMSNORM_QUANT) {
-            raw[i] = packed;
-          } else {
-            st_stream16(yrow + col, packed);
+        }
+        if (!done) {
+#pragma unroll
+          for (int i = 0; i < VPT; ++i) {
+            const int v = i * TPR + t;
+            if (row_ok && v < nvec) {
+              float f[VEC];
+              P::unpack(raw[i], f);
+              const int64_t col = static_cast<int64_t>(v) * VEC;
+              float wv[VEC];
+              load_param_vec<VEC>(p.w, p.w_dtype, col, wv);
+#pragma unroll
+              for (int j = 0; j < VEC; ++j)
+                f[j] = __fmul_rn(wv[j], P::round(__fmul_rn(f[j], rstd)));
+              emit(i, col, P::pack(f));
+            }
           }
         }
       }
@@ -211,24 +266,32 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256))
       const QuantRow qr = make_quant_row(am);
       if (row_ok && t == 0) p.scales[row] = qr.scale;
       int8_t* crow = p.codes + (row_ok ? row : 0) * p.codes_stride;
+      auto encode_row = [&](auto mode_tag) {
+        constexpr int MODE = decltype(mode_tag)::value;
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = i * TPR + t;
-        if (row_ok && v < nvec) {
-          float2 f2[VEC / 2];
-          P::unpack2(raw[i], f2);
-          uint32_t yb[VEC];
+        for (int i = 0; i < VPT; ++i) {
+          const int v = i * TPR + t;
+          if (row_ok && v < nvec) {
+            float2 f2[VEC / 2];
+            P::unpack2(raw[i], f2);
+            uint32_t yb[VEC];
 #pragma unroll
-          for (int j = 0; j < VEC / 2; ++j) quant_pair(f2[j], qr, yb[2 * j], yb[2 * j + 1]);
-          int8_t* dst = crow + static_cast<int64_t>(v) * VEC;
-          if constexpr (VEC == 8) {
-            st_stream8(dst, make_uint2(pack_low_bytes(yb[0], yb[1], yb[2], yb[3]),
-                                       pack_low_bytes(yb[4], yb[5], yb[6], yb[7])));
-          } else {
-            st_stream4(dst, pack_low_bytes(yb[0], yb[1], yb[2], yb[3]));
+            for (int j = 0; j < VEC / 2; ++j)
+              quant_pair<MODE, (VEC == 8)>(f2[j], qr, yb[2 * j], yb[2 * j + 1]);
+            int8_t* dst = crow + static_cast<int64_t>(v) * VEC;
+            if constexpr (VEC == 8) {
+              st_stream8(dst, make_uint2(pack_low_bytes(yb[0], yb[1], yb[2], yb[3]),
+                                         pack_low_bytes(yb[4], yb[5], yb[6], yb[7])));
+            } else {
+              st_stream4(dst, pack_low_bytes(yb[0], yb[1], yb[2], yb[3]));
+            }
           }
         }
-      }
+      };
+      // the mode is uniform over the row: one branch per row, not one per value
+      if (qr.mode == 1) encode_row(std::integral_constant<int, 1>{});
+      else if (qr.mode == 2) encode_row(std::integral_constant<int, 2>{});
+      else encode_row(std::integral_constant<int, 0>{});
     }
   }
 }
@@ -238,7 +301,7 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256))
 template <int OP, typename T>
 __global__ void __launch_bounds__(256) row_kernel_generic(const RowParams p) {
   using P = Pack<T>;
-  __shared__ float red[2][32];
+  __shared__ __align__(16) float red[2][32];
   int sel = 0;
   constexpr bool HAS_QUANT = (OP == OP_QUANT || OP == OP_RMSNORM_QUANT);
   for (int64_t row = blockIdx.x; row < p.R; row += gridDim.x) {
@@ -351,11 +414,11 @@ static int launch_row(const RowParams& p, cudaStream_t stream) {
     if (nvec <= 32) return launch_cfg<OP, T, 32, 1>(p, stream);
     if (nvec <= 64) return launch_cfg<OP, T, 32, 2>(p, stream);
     if (nvec <= 128) return launch_cfg<OP, T, 32, 4>(p, stream);
-    if (nvec <= 256) return launch_cfg<OP, T, 32, 8>(p, stream);
-    if (nvec <= 512) return launch_cfg<OP, T, 32, 16>(p, stream);
-    if (nvec <= 1024) return launch_cfg<OP, T, 128, 8>(p, stream);
-    if (nvec <= 2048) return launch_cfg<OP, T, 256, 8>(p, stream);
-    if (nvec <= 4096) return launch_cfg<OP, T, 512, 8>(p, stream);
+    if (nvec <= 256) return launch_cfg<OP, T, TRX_ROW256_TPR, TRX_ROW256_VPT>(p, stream);
+    if (nvec <= 512) return launch_cfg<OP, T, TRX_ROW512_TPR, TRX_ROW512_VPT>(p, stream);
+    if (nvec <= 1024) return launch_cfg<OP, T, 256, 4>(p, stream);
+    if (nvec <= 2048) return launch_cfg<OP, T, 512, 4>(p, stream);
+    if (nvec <= 4096) return launch_cfg<OP, T, 1024, 4>(p, stream);
     if (nvec <= 8192) return launch_cfg<OP, T, 1024, 8>(p, stream);
     return launch_cfg<OP, T, 1024, 16>(p, stream);
   }

@@ -190,10 +190,16 @@ class FastRoPEPositionEmbedding(nn.Module):
         self.register_buffer("inv_freq", inv_freq, persistent=False)
 
     def forward(self, x: torch.Tensor, seq_len: Optional[int] = None):
+        """(cos, sin) of shape (seq_len, dim) in x's dtype. The angles are always built in
+        fp32 from `base` and `dim`: the reference builds them from its `inv_freq` buffer, which
+        `module.to(torch.bfloat16)` silently rounds to bf16 (positions above 256 then collapse
+        onto each other); this mirror keeps the buffer for state-dict compatibility only."""
         if seq_len is None:
             seq_len = x.shape[-2]
-        pos = torch.arange(seq_len, device=x.device, dtype=self.inv_freq.dtype)
-        angles = torch.outer(pos, self.inv_freq)
+        inv_freq = 1.0 / self.base ** (
+            torch.arange(0, self.dim, 2, device=x.device, dtype=torch.float32) / self.dim)
+        pos = torch.arange(seq_len, device=x.device, dtype=torch.float32)
+        angles = torch.outer(pos, inv_freq)
         table = torch.cat((angles, angles), dim=-1)
         return table.cos().to(x.dtype), table.sin().to(x.dtype)
 
