@@ -166,6 +166,37 @@ int trx_attn_fwd(const void* q, const void* k, const void* v, void* out, float* 
                  int64_t window_left, int64_t window_right, int dtype, void* workspace,
                  size_t workspace_bytes, void* stream);
 
+/*
+ * trx_attn_fwd for callers that cannot provide a workspace. No counterpart in the reference.
+ *
+ * Who needs it: hosts that pass pointers in but cannot create device memory when the call is
+ * made — an inference-engine plugin whose memory plan is fixed when the engine is built and
+ * whose execute hook must not allocate, or a process whose device memory is owned entirely by
+ * a broker. This entry point performs no cudaMalloc / cudaFree and calls no allocating library
+ * routine; the kernel's 256-byte scratch block lives in a static array inside the library
+ * (256 bytes on every GPU that loads the library, kept until the process exits).
+ *
+ * Same arguments and results as trx_attn_fwd, minus the workspace, plus
+ *   status_out_or_null: optional 4-byte destination (device or pinned host memory) that
+ *   receives the kernel's status word in stream order; 0 means no bounded wait gave up.
+ * Limit: the static block is 256 bytes, which is what the kernel needs for EVERY problem size
+ * trx_attn_fwd accepts; if the library's own requirement ever exceeds the block the call
+ * returns TRX_ERR_WORKSPACE and launches nothing.
+ * The first call on each device looks up the block's device address (with that device
+ * current); make that first call outside of any stream capture.
+ * All calls on a device share the one block, which still holds the previous call's contents:
+ * the entry point zeroes it in stream order before each launch. Two calls whose work overlaps
+ * on the GPU (different streams, or different host threads feeding different streams) race
+ * on it; issue them on one stream or serialise them.
+ */
+int trx_attn_fwd_static_scratch(const void* q, const void* k, const void* v, void* out,
+                                float* lse_or_null, const float* slopes_or_null, int64_t B,
+                                int64_t Sq, int64_t Sk, int64_t Hq, int64_t Hk, int64_t D,
+                                const int64_t q_strides[3], const int64_t k_strides[3],
+                                const int64_t v_strides[3], const int64_t o_strides[3],
+                                float scale, int causal, int64_t window_left, int64_t window_right,
+                                int dtype, unsigned int* status_out_or_null, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

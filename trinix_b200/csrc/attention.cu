@@ -21,6 +21,8 @@
 // own copies and MMAs (bounded again), frees its TMEM and returns.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace trx {
@@ -839,4 +841,65 @@ extern "C" int trx_attn_fwd(const void* q, const void* k, const void* v, void* o
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 128) return is_bf16 ? launch_attn<128, true>(p, s) : launch_attn<128, false>(p, s);
   return is_bf16 ? launch_attn<64, true>(p, s) : launch_attn<64, false>(p, s);
+}
+
+// ------------------------------------------------------------------------------------------
+// Attention without a caller-supplied workspace
+// ------------------------------------------------------------------------------------------
+// Some hosts can hand this library pointers but cannot produce device memory of their own at
+// call time: an inference-engine plugin whose memory plan was frozen when the engine was
+// built and whose execute hook must not allocate, or a process in which a memory broker owns
+// the whole device and hands out nothing on demand. For them the attention kernel's scratch
+// (its 256-byte status / scheduler block) lives in the library image instead: one static
+// array per loaded copy of the library, i.e. 256 bytes on every GPU that loads it, held until
+// the process exits.
+constexpr size_t ATT_STATIC_SCRATCH_BYTES = 256;
+static __device__ __align__(256) unsigned char g_attn_static_scratch[ATT_STATIC_SCRATCH_BYTES];
+
+// In host code `g_attn_static_scratch` is only a handle for the runtime, not an address a
+// kernel could use; the device address is looked up once per device, with that device
+// current, and cached here.
+static std::mutex g_scratch_mutex;
+static void* g_scratch_addr[64] = {nullptr};
+
+static int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TRX_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_attn_static_scratch) != cudaSuccess || ptr == nullptr)
+      return TRX_ERR_CUDA;
+    g_scratch_addr[dev] = ptr;
+  }
+  *out = g_scratch_addr[dev];
+  return TRX_OK;
+}
+
+extern "C" int trx_attn_fwd_static_scratch(
+    const void* q, const void* k, const void* v, void* out, float* lse_or_null,
+    const float* slopes_or_null, int64_t B, int64_t Sq, int64_t Sk, int64_t Hq, int64_t Hk,
+    int64_t D, const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+    const int64_t o_strides[3], float scale, int causal, int64_t window_left, int64_t window_right,
+    int dtype, unsigned int* status_out_or_null, void* stream) {
+  // The kernel's scratch need does not grow with the problem; should a later revision of the
+  // kernel ever ask for more than the static array holds, refuse instead of overrunning it.
+  if (trx_attn_workspace_bytes() > ATT_STATIC_SCRATCH_BYTES) return TRX_ERR_WORKSPACE;
+  void* scratch = nullptr;
+  const int rc = static_scratch_for_current_device(&scratch);
+  if (rc != TRX_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left in it. The status word must start at
+  // zero (a non-zero word makes the kernel skip its work), so clear the block in stream order.
+  if (cudaMemsetAsync(scratch, 0, ATT_STATIC_SCRATCH_BYTES, s) != cudaSuccess) return TRX_ERR_CUDA;
+  const int launched =
+      trx_attn_fwd(q, k, v, out, lse_or_null, slopes_or_null, B, Sq, Sk, Hq, Hk, D, q_strides,
+                   k_strides, v_strides, o_strides, scale, causal, window_left, window_right, dtype,
+                   scratch, ATT_STATIC_SCRATCH_BYTES, stream);
+  if (launched != TRX_OK) return launched;
+  if (status_out_or_null != nullptr &&
+      cudaMemcpyAsync(status_out_or_null, scratch, sizeof(unsigned int), cudaMemcpyDefault, s) !=
+          cudaSuccess)
+    return TRX_ERR_CUDA;
+  return TRX_OK;
 }
