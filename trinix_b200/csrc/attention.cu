@@ -135,26 +135,46 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                    bar)
                : "memory");
 }
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
+// D[tmem] = A[smem] * B[smem]  (first) / D[tmem] += A[smem] * B[smem]  (acc)
+__device__ __forceinline__ void mma_ss_first(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                             uint32_t idesc) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 p, 0, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       :
-      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc)
       : "memory");
 }
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_ss_acc(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                           uint32_t idesc) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc)
+      : "memory");
+}
+// D[tmem] = A[tmem] * B[smem]  (first) / D[tmem] += A[tmem] * B[smem]  (acc)
+__device__ __forceinline__ void mma_ts_first(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                             uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, 0, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       :
-      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                           uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
       : "memory");
 }
 
@@ -163,11 +183,20 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
   if constexpr (BF16) return Pack<__nv_bfloat16>::pack2(lo, hi);
   else return Pack<__half>::pack2(lo, hi);
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 // 2^x on the special-function unit; 2^-inf = +0.
 __device__ __forceinline__ float fast_exp2(float x) {
+#if defined(TRX_ATT_EXPERIMENT) && TRX_ATT_EXPERIMENT == 3
+  return fmaf(x, 0.001f, 1.0f);  // timing experiment: no special-function unit
+#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+#endif
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane (base lane + t).
@@ -327,7 +356,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar(B_SFULL + t), 1);
-      mbar_init(bar(B_PFULL + t), ATT_BM);
+      mbar_init(bar(B_PFULL + t), ATT_BM / 32);  // one arrival per softmax warp
       mbar_init(bar(B_ODONE + t), 1);
     }
     mbar_init(bar(B_DRAIN), 1);
@@ -398,19 +427,36 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         return mbar_wait(bar(B_KVFULL + fill % ATT_STAGES), (fill / ATT_STAGES) & 1, abort_flag,
                          p.status, ATT_ST_MMA);
       };
+      // Descriptors differ only in their 14-bit start-address field (address >> 4), which is
+      // the low part of the low word: build the constant part once and add offsets with one
+      // 32-bit add per operand, so that the issuing thread keeps ahead of the tensor pipe.
+      const uint64_t desc_k_major = make_desc(0, 16, 1024);            // K-major, SBO 1 KB
+      const uint64_t desc_mn_major = make_desc(0, L::CHUNK_BYTES, 1024);  // MN-major V
+      const uint32_t dk_hi = static_cast<uint32_t>(desc_k_major >> 32);
+      const uint32_t dk_lo = static_cast<uint32_t>(desc_k_major);
+      const uint32_t dv_hi = static_cast<uint32_t>(desc_mn_major >> 32);
+      const uint32_t dv_lo = static_cast<uint32_t>(desc_mn_major);
+      auto desc_of = [](uint32_t lo, uint32_t hi) {
+        return (static_cast<uint64_t>(hi) << 32) | lo;
+      };
+      const uint32_t q_lo0 = dk_lo + ((sbase + L::Q_OFF) >> 4);
+      const uint32_t kv_lo0 = (sbase + L::KV_OFF) >> 4;
       auto issue_qk = [&](int t, int fill) {
         if (!q_ready[t]) {
           if (!mbar_wait(bar(B_QFULL + t), 0, abort_flag, p.status, ATT_ST_MMA)) return false;
           q_ready[t] = true;
         }
         tc_fence_after();
-        const uint32_t qa = sbase + L::Q_OFF + t * L::TILE_BYTES;
-        const uint32_t ka = sbase + L::KV_OFF + (fill % ATT_STAGES) * L::TILE_BYTES;
+        const uint32_t qlo = q_lo0 + t * (L::TILE_BYTES >> 4);
+        const uint32_t klo = dk_lo + kv_lo0 + (fill % ATT_STAGES) * (L::TILE_BYTES >> 4);
+        const uint32_t d_tmem = tmem_base + t * ATT_BN;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * L::CHUNK_BYTES + (kk % 4) * 32;
-          mma_ss(tmem_base + t * ATT_BN, make_desc(qa + off, 16, 1024),
-                 make_desc(ka + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+          const uint32_t off = ((kk / 4) * L::CHUNK_BYTES + (kk % 4) * 32) >> 4;
+          if (kk == 0)
+            mma_ss_first(d_tmem, desc_of(qlo + off, dk_hi), desc_of(klo + off, dk_hi), idesc_qk);
+          else
+            mma_ss_acc(d_tmem, desc_of(qlo + off, dk_hi), desc_of(klo + off, dk_hi), idesc_qk);
         }
         tc_commit(bar(B_SFULL + t));
         return true;
@@ -419,12 +465,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         if (!mbar_wait(bar(B_PFULL + t), it[t] & 1, abort_flag, p.status, ATT_ST_MMA))
           return false;
         tc_fence_after();
-        const uint32_t va = sbase + L::KV_OFF + (fill % ATT_STAGES) * L::TILE_BYTES;
+        const uint32_t vlo = dv_lo + kv_lo0 + (fill % ATT_STAGES) * (L::TILE_BYTES >> 4);
+        const uint32_t d_tmem = tmem_base + 2 * ATT_BN + t * ATT_BN;
+        const uint32_t a_tmem = tmem_base + t * ATT_BN;
 #pragma unroll
         for (int kk = 0; kk < ATT_BN / 16; ++kk) {
-          mma_ts(tmem_base + 2 * ATT_BN + t * ATT_BN, tmem_base + t * ATT_BN + kk * 8,
-                 make_desc(va + kk * 2048, L::CHUNK_BYTES, 1024), idesc_pv,
-                 (accumulate || kk > 0) ? 1u : 0u);
+          const uint64_t vd = desc_of(vlo + kk * (2048 >> 4), dv_hi);
+          if (kk == 0 && !accumulate)
+            mma_ts_first(d_tmem, a_tmem + kk * 8, vd, idesc_pv);
+          else
+            mma_ts_acc(d_tmem, a_tmem + kk * 8, vd, idesc_pv);
         }
         tc_commit(bar(B_ODONE + t));
         ++it[t];
@@ -504,12 +554,33 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                       mbar_wait(bar(B_SFULL + t), itn & 1, abort_flag, p.status, ATT_ST_SOFTMAX));
       if (!ok) break;
       tc_fence_after();
+#if defined(TRX_ATT_EXPERIMENT) && TRX_ATT_EXPERIMENT == 1
+      // timing experiment: no softmax at all
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_PFULL + t));
+      continue;
+#endif
       uint32_t sr[ATT_BN];
       tmem_ld32<0>(s_addr + 0, sr);
       tmem_ld32<32>(s_addr + 32, sr);
       tmem_ld32<64>(s_addr + 64, sr);
       tmem_ld32<96>(s_addr + 96, sr);
       tmem_wait_ld();
+#if defined(TRX_ATT_EXPERIMENT) && TRX_ATT_EXPERIMENT == 2
+      // timing experiment: TMEM load + convert + TMEM store, no max / exp
+#pragma unroll
+      for (int c = 0; c < ATT_BN; c += 2)
+        sr[c / 2] = pack16<BF16>(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+      tmem_st32<0>(s_addr + 0, sr);
+      tmem_st32<32>(s_addr + 32, sr);
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_PFULL + t));
+      l_run = 1.0f;
+      continue;
+#endif
 
       const bool need_mask = (c0 + ATT_BN - 1 > hi_min) || (c0 < lo_max);
       // ALiBi on a tile that lies entirely on one side of the diagonal is linear in the
@@ -520,7 +591,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         if (c0 + ATT_BN - 1 <= row0) alibi_sgn = 1;   // every key at or before every query
         else if (c0 >= row1) alibi_sgn = -1;          // every key at or after every query
       }
-      const bool general = need_mask || (has_alibi && alibi_sgn == 0) || !(sl2 > 0.0f);
+      // general path: a tile that straddles the diagonal under ALiBi, or a non-positive scale
+      const bool general = (has_alibi && alibi_sgn == 0) || !(sl2 > 0.0f);
       float m_tile = -INFINITY;
       float off = 0.0f;  // fast path: x = t * sl2 + off
       if (general) {
@@ -537,6 +609,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
           m_tile = fmaxf(m_tile, x);
         }
       } else {
+        if (need_mask) {
+          // boundary tile: hide keys outside [lo_i, hi_i] in the raw domain (sl2 > 0 keeps
+          // -inf at -inf), then continue on the fast path
+          const int lo_c = lo_i - c0, hi_c = hi_i - c0;
+#pragma unroll
+          for (int c = 0; c < ATT_BN; ++c)
+            if (c < lo_c || c > hi_c) sr[c] = 0xff800000u;  // -inf
+        }
         if (alibi_sgn != 0) {
           const float sk = static_cast<float>(alibi_sgn) * slope2;
           const float kc = __fdividef(sk, sl2);
@@ -547,13 +627,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         }
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int c = 0; c < ATT_BN; c += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(sr[c + 0]));
-          mx1 = fmaxf(mx1, __uint_as_float(sr[c + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(sr[c + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(sr[c + 3]));
+        for (int c = 0; c < ATT_BN; c += 8) {
+          mx0 = max3(mx0, __uint_as_float(sr[c + 0]), __uint_as_float(sr[c + 1]));
+          mx1 = max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+          mx2 = max3(mx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
+          mx3 = max3(mx3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
         }
-        m_tile = fmaf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), sl2, off);
+        const float mraw = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        m_tile = (mraw == -INFINITY) ? -INFINITY : fmaf(mraw, sl2, off);
       }
 
       // lazy rescale: keep the old reference max unless the new one is much larger
@@ -615,7 +696,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(B_PFULL + t));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_PFULL + t));
     }
 
     // ---- epilogue: O / l -> global --------------------------------------------------

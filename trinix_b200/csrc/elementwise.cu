@@ -2,8 +2,8 @@
 // in one launch) and per-row int8 dequantisation.
 //
 // All three are pure HBM streams. Each thread moves 16-byte vectors with
-// streaming loads/stores and keeps several independent loads in flight (four
-// rows per thread for GLU/dequant; the two halves of a head vector plus the
+// streaming loads/stores and keeps several independent loads in flight (four / eight
+// rows per thread for GLU / dequant; the two halves of a head vector plus the
 // table entries for RoPE). Grids are 2-D (column-vector block, row block) so no
 // thread ever divides to find its row. Shapes or pointers that do not fit the
 // vector path take a scalar kernel.
@@ -142,53 +142,79 @@ struct RopeParams {
 // the activation dtype and every product and the sum are rounded to it, again
 // matching that path op for op. Multiplies and adds are kept separate (no FMA
 // contraction) so both modes reproduce its results exactly.
+//
+// Work split: a thread owns one (token, 8-column slice of the half dim) and walks over all
+// heads of q and then k, four heads per step, so the slice's cos/sin values are loaded once
+// and eight independent 16-byte loads are in flight per thread. Neighbouring threads cover
+// neighbouring slices of the same token, i.e. whole 128-byte lines of each head vector.
+constexpr int ROPE_HEADS_PER_STEP = 4;
+
 template <typename T, bool TABLE_F32>
-__global__ void __launch_bounds__(1024) rope_kernel(const RopeParams p) {
+__global__ void __launch_bounds__(128) rope_kernel(const RopeParams p, int vec_per_head,
+                                                   int64_t tokens) {
   using P = Pack<T>;
   constexpr int VEC = P::VEC;
   const int half = p.D / 2;
-  const int vec_per_head = half / VEC;
-  const int items = (p.Hq + p.Hk) * vec_per_head;
-  const int64_t token = blockIdx.x;
+  const int tok_per_cta = blockDim.x / vec_per_head;
+  const int64_t token = static_cast<int64_t>(blockIdx.x) * tok_per_cta + threadIdx.x / vec_per_head;
+  if (token >= tokens) return;
+  const int j = (threadIdx.x % vec_per_head) * VEC;
   const int64_t b = token / p.S;
   const int64_t s = token - b * p.S;
-  for (int it = threadIdx.x; it < items; it += blockDim.x) {
-    const int h_all = it / vec_per_head;
-    const int j = (it - h_all * vec_per_head) * VEC;
-    const bool is_q = h_all < p.Hq;
-    const int h = is_q ? h_all : h_all - p.Hq;
-    const int64_t* st = is_q ? p.qs : p.ks;
-    const int64_t* ost = is_q ? p.qos : p.kos;
-    const T* src = reinterpret_cast<const T*>(is_q ? p.q : p.k) + b * st[0] + s * st[1] +
-                   static_cast<int64_t>(h) * st[2];
-    T* dst = reinterpret_cast<T*>(is_q ? p.qo : p.ko) + b * ost[0] + s * ost[1] +
-             static_cast<int64_t>(h) * ost[2];
-    const uint4 r1 = ld_stream16(src + j);
-    const uint4 r2 = ld_stream16(src + half + j);
-    float c[VEC], sn[VEC];
-    if constexpr (TABLE_F32) {
-      load_param_vec<VEC>(p.cos_t, TRX_F32, s * p.table_stride + j, c);
-      load_param_vec<VEC>(p.sin_t, TRX_F32, s * p.table_stride + j, sn);
-    } else {
-      load_param_vec<VEC>(p.cos_t, P::DTYPE, s * p.table_stride + j, c);
-      load_param_vec<VEC>(p.sin_t, P::DTYPE, s * p.table_stride + j, sn);
-    }
-    float x1[VEC], x2[VEC], o1[VEC], o2[VEC];
-    P::unpack(r1, x1);
-    P::unpack(r2, x2);
+
+  float c[VEC], sn[VEC];
+  if constexpr (TABLE_F32) {
+    load_param_vec<VEC>(p.cos_t, TRX_F32, s * p.table_stride + j, c);
+    load_param_vec<VEC>(p.sin_t, TRX_F32, s * p.table_stride + j, sn);
+  } else {
+    load_param_vec<VEC>(p.cos_t, P::DTYPE, s * p.table_stride + j, c);
+    load_param_vec<VEC>(p.sin_t, P::DTYPE, s * p.table_stride + j, sn);
+  }
+  if (p.inverse) {
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) {
-      const float sv = p.inverse ? -sn[e] : sn[e];
-      if constexpr (TABLE_F32) {
-        o1[e] = __fadd_rn(__fmul_rn(x1[e], c[e]), __fmul_rn(-x2[e], sv));
-        o2[e] = __fadd_rn(__fmul_rn(x2[e], c[e]), __fmul_rn(x1[e], sv));
-      } else {
-        o1[e] = __fadd_rn(P::round(__fmul_rn(x1[e], c[e])), P::round(__fmul_rn(-x2[e], sv)));
-        o2[e] = __fadd_rn(P::round(__fmul_rn(x2[e], c[e])), P::round(__fmul_rn(x1[e], sv)));
+    for (int e = 0; e < VEC; ++e) sn[e] = -sn[e];
+  }
+
+  const int H = p.Hq + p.Hk;
+  for (int h0 = 0; h0 < H; h0 += ROPE_HEADS_PER_STEP) {
+    uint4 r1[ROPE_HEADS_PER_STEP], r2[ROPE_HEADS_PER_STEP];
+    T* dst[ROPE_HEADS_PER_STEP];
+#pragma unroll
+    for (int u = 0; u < ROPE_HEADS_PER_STEP; ++u) {
+      const int h_all = h0 + u;
+      if (h_all < H) {
+        const bool is_q = h_all < p.Hq;
+        const int h = is_q ? h_all : h_all - p.Hq;
+        const int64_t* st = is_q ? p.qs : p.ks;
+        const int64_t* ost = is_q ? p.qos : p.kos;
+        const T* src = reinterpret_cast<const T*>(is_q ? p.q : p.k) + b * st[0] + s * st[1] +
+                       static_cast<int64_t>(h) * st[2];
+        dst[u] = reinterpret_cast<T*>(is_q ? p.qo : p.ko) + b * ost[0] + s * ost[1] +
+                 static_cast<int64_t>(h) * ost[2];
+        r1[u] = ld_stream16(src + j);
+        r2[u] = ld_stream16(src + half + j);
       }
     }
-    st_stream16(dst + j, P::pack(o1));
-    st_stream16(dst + half + j, P::pack(o2));
+#pragma unroll
+    for (int u = 0; u < ROPE_HEADS_PER_STEP; ++u) {
+      if (h0 + u < H) {
+        float x1[VEC], x2[VEC], o1[VEC], o2[VEC];
+        P::unpack(r1[u], x1);
+        P::unpack(r2[u], x2);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          if constexpr (TABLE_F32) {
+            o1[e] = __fadd_rn(__fmul_rn(x1[e], c[e]), __fmul_rn(-x2[e], sn[e]));
+            o2[e] = __fadd_rn(__fmul_rn(x2[e], c[e]), __fmul_rn(x1[e], sn[e]));
+          } else {
+            o1[e] = __fadd_rn(P::round(__fmul_rn(x1[e], c[e])), P::round(__fmul_rn(-x2[e], sn[e])));
+            o2[e] = __fadd_rn(P::round(__fmul_rn(x2[e], c[e])), P::round(__fmul_rn(x1[e], sn[e])));
+          }
+        }
+        st_stream16(dst[u] + j, P::pack(o1));
+        st_stream16(dst[u] + half + j, P::pack(o2));
+      }
+    }
   }
 }
 
@@ -242,11 +268,13 @@ static int launch_rope(const RopeParams& p, int64_t B, cudaStream_t stream) {
   const int64_t tokens = B * p.S;
   if (tokens == 0) return TRX_OK;
   if (tokens >= (1ll << 31)) return TRX_ERR_SHAPE;
-  if (vec_ok) {
-    const int items = (p.Hq + p.Hk) * (half / VEC);
-    int threads = ((items + 31) / 32) * 32;
-    if (threads > 1024) threads = 1024;
-    rope_kernel<T, TABLE_F32><<<static_cast<unsigned>(tokens), threads, 0, stream>>>(p);
+  const int vec_per_head = vec_ok ? half / VEC : 0;
+  if (vec_ok && vec_per_head <= 128) {
+    const int tok_per_cta = 128 / vec_per_head;
+    const int threads = tok_per_cta * vec_per_head;
+    const int64_t blocks = (tokens + tok_per_cta - 1) / tok_per_cta;
+    rope_kernel<T, TABLE_F32><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+        p, vec_per_head, tokens);
   } else {
     rope_kernel_scalar<T, TABLE_F32><<<static_cast<unsigned>(tokens), 256, 0, stream>>>(p);
   }
@@ -256,11 +284,14 @@ static int launch_rope(const RopeParams& p, int64_t B, cudaStream_t stream) {
 // ----------------------------------------------------------------------------
 // Dequantise
 // ----------------------------------------------------------------------------
-constexpr int DQ_ROWS_PER_THREAD = 4;
+constexpr int DQ_ROWS_PER_THREAD = 8;
 constexpr int DQ_THREADS = 128;
 
-__device__ __forceinline__ float code_at(uint32_t word, int byte) {
-  return static_cast<float>(static_cast<int>(static_cast<int8_t>((word >> (8 * byte)) & 0xffu)));
+// int8 -> fp32 without a convert instruction: place (code ^ 0x80) in the low mantissa byte
+// of 2^23 and subtract 2^23 + 128 (exact).
+__device__ __forceinline__ float code_at(uint32_t word_xor80, int byte) {
+  const uint32_t bits = __byte_perm(word_xor80, 0x4B000000u, 0x7650 + byte);  // {b, 0, 0, 0x4B}
+  return __uint_as_float(bits) - 8388736.0f;
 }
 
 // 16 codes per thread per row: one 16-byte load, (16 * sizeof(T)) bytes of stores.
@@ -289,7 +320,8 @@ __global__ void __launch_bounds__(DQ_THREADS)
     for (int i = 0; i < DQ_ROWS_PER_THREAD; ++i) {
       const int64_t r = r0 + i;
       if (r < R) {
-        const uint32_t w[4] = {c[i].x, c[i].y, c[i].z, c[i].w};
+        const uint32_t w[4] = {c[i].x ^ 0x80808080u, c[i].y ^ 0x80808080u, c[i].z ^ 0x80808080u,
+                               c[i].w ^ 0x80808080u};
         float f[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) f[j] = __fmul_rn(code_at(w[j >> 2], j & 3), sc[i]);
@@ -326,8 +358,14 @@ static int launch_dequant(const int8_t* codes, const float* scales, void* y, int
   if (vec_ok) {
     const int nvec16 = static_cast<int>(C / 16);
     const int64_t row_blocks = (R + DQ_ROWS_PER_THREAD - 1) / DQ_ROWS_PER_THREAD;
-    dim3 grid((nvec16 + DQ_THREADS - 1) / DQ_THREADS,
-              static_cast<unsigned>(row_blocks < 65535 ? row_blocks : 65535));
+    // One resident wave: about 8 CTAs of 128 threads per SM in total, each walking over
+    // row blocks, so that a short launch is not split into a full and a nearly empty wave.
+    const int64_t col_blocks = (nvec16 + DQ_THREADS - 1) / DQ_THREADS;
+    int64_t y_blocks = (148 * 8 + col_blocks - 1) / col_blocks;
+    if (y_blocks > row_blocks) y_blocks = row_blocks;
+    if (y_blocks > 65535) y_blocks = 65535;
+    if (y_blocks < 1) y_blocks = 1;
+    dim3 grid(static_cast<unsigned>(col_blocks), static_cast<unsigned>(y_blocks));
     dequant_kernel<T><<<grid, DQ_THREADS, 0, stream>>>(codes, scales, static_cast<T*>(y), R,
                                                        nvec16, cs, ys);
   } else {
