@@ -333,6 +333,45 @@ def run_reference_arm(args):
     }))
 
 
+def profile_case(name: str):
+    """A handful of eager launches on benchmark-sized (but < 2 GB) inputs, for profiler captures:
+    `ncu ... python bench.py --profile-case attention`. Prints nothing but a completion line."""
+    from trinix_b200 import ops
+    import trinix_b200 as T
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    g = torch.Generator(device=device).manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, generator=g, device=device, dtype=torch.float32).bfloat16()
+    if name == "int8":
+        acts = [rnd(ACT_ROWS, ACT_SHAPE[2]) for _ in range(2)]  # 2 x 256 MB, each pass misses L2
+        xq = [rnd(*QUANT_SHAPE) for _ in range(3)]
+        w = torch.ones(ACT_SHAPE[2], device=device, dtype=torch.bfloat16)
+        for i in range(4):
+            ops.rmsnorm_quantize(acts[i % 2], w, 1e-6)
+            c, sc = ops.quantize_rowwise(xq[i % 3])
+            ops.dequantize_rowwise(c, sc, torch.bfloat16)
+    elif name == "stream":
+        acts = [rnd(ACT_ROWS, ACT_SHAPE[2]) for _ in range(2)]
+        w = torch.ones(ACT_SHAPE[2], device=device, dtype=torch.bfloat16)
+        b = torch.zeros(ACT_SHAPE[2], device=device, dtype=torch.bfloat16)
+        q, k = rnd(8, 2048, 32, 128), rnd(8, 2048, 8, 128)
+        inv = 1.0 / 10000.0 ** (torch.arange(0, 128, 2, device=device).float() / 128)
+        fr = torch.outer(torch.arange(2048, device=device).float(), inv)
+        cos, sin = torch.cat([fr, fr], -1).cos(), torch.cat([fr, fr], -1).sin()
+        xg = rnd(8192, 22016)
+        for i in range(3):
+            ops.rmsnorm(acts[i % 2], w, 1e-6)
+            ops.layernorm(acts[i % 2], w, b, 1e-5)
+            ops.rope(q, k, cos, sin)
+            ops.glu(xg, "swiglu")
+    else:
+        q, k, v = rnd(2, 4096, 32, 128), rnd(2, 4096, 8, 128), rnd(2, 4096, 8, 128)
+        for _ in range(4):
+            ops.attention(q, k, v, causal=True)
+    torch.cuda.synchronize()
+    print(f"profile case {name} done; attention status word {T.attention_status(device)}")
+
+
 # ----------------------------------------------------------------------------- main arm
 def main():
     ap = argparse.ArgumentParser()
@@ -342,7 +381,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-kernel table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-case", choices=["int8", "stream", "attention"],
+                    help="launch a few kernels of one family eagerly and exit (for ncu captures)")
     args = ap.parse_args()
+    if args.profile_case:
+        profile_case(args.profile_case)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
         return
