@@ -1,13 +1,15 @@
 // Attention forward for sm_100a: softmax(scale * Q K^T + bias) V with online softmax.
 //
 // One CTA owns 256 query rows of one (batch, head): two 128-row Q tiles that ping-pong
-// on the tensor pipe. Roles (320 threads):
-//   warps 0-3  softmax group 0 (thread t owns row t of Q tile 0 = TMEM lane t)
-//   warps 4-7  softmax group 1 (Q tile 1)
-//   warp  8    TMA producer: Q once, then K and V tiles through a 4-stage shared-memory ring
-//              (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
-//   warp  9    MMA issuer: tcgen05.mma kind::f16, S = Q K^T (both operands from shared memory)
-//              and O += P V (P read from TMEM, V from shared memory, MN-major)
+// on the tensor pipe. Roles (576 threads):
+//   warps 0-7   softmax of Q tile 0: warp w owns the 16 rows (= TMEM lanes) 32*(w%4)+16*(w/4)..,
+//               read in the 16x256b fragment shape: a quad of threads shares a row, a thread
+//               holds 2 rows x 32 columns, row maxima cost two shuffles
+//   warps 8-15  softmax of Q tile 1, same split
+//   warp  16    TMA producer: Q once, then K and V tiles through a 4-stage shared-memory ring
+//               (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
+//   warp  17    MMA issuer: tcgen05.mma kind::f16, S = Q K^T (both operands from shared memory)
+//               and O += P V (P read from TMEM, V from shared memory, MN-major)
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P (16-bit) overwrites the
 // first 64 columns of its S. The softmax groups read S with tcgen05.ld, exponentiate with
 // exp2 (scale*log2e folded into one FMA, ALiBi as one more), write P back with tcgen05.st,
@@ -31,10 +33,12 @@ constexpr int ATT_BM = 128;       // rows per Q tile
 constexpr int ATT_BN = 128;       // keys per KV tile
 constexpr int ATT_NQ = 2;         // Q tiles per CTA
 constexpr int ATT_STAGES = 4;     // KV ring depth (K and V tiles alternate)
-constexpr int ATT_THREADS = 320;
+constexpr int ATT_SM_WARPS = 16;    // softmax warps: two warpgroups per Q tile, half a row per thread
+constexpr int ATT_THREADS = (ATT_SM_WARPS + 2) * 32;
 constexpr uint32_t ATT_WAIT_LIMIT = 1u << 26;  // hard cap on polls per wait
 constexpr uint64_t ATT_WAIT_NS = 400ull * 1000 * 1000;  // wall-time budget of one wait
 constexpr float ATT_LAZY_RESCALE = 8.0f;       // log2 units
+constexpr int SM_COLS = ATT_BN / 2;            // score columns owned by one softmax thread
 
 enum AttnStatus : unsigned {
   ATT_ST_PRODUCER = 1u,
@@ -190,13 +194,9 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 }
 // 2^x on the special-function unit; 2^-inf = +0.
 __device__ __forceinline__ float fast_exp2(float x) {
-#if defined(TRX_ATT_EXPERIMENT) && TRX_ATT_EXPERIMENT == 3
-  return fmaf(x, 0.001f, 1.0f);  // timing experiment: no special-function unit
-#else
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-#endif
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane (base lane + t).
@@ -232,6 +232,42 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[N]
         "r"(r[OFF + 24]), "r"(r[OFF + 25]), "r"(r[OFF + 26]), "r"(r[OFF + 27]), "r"(r[OFF + 28]),
         "r"(r[OFF + 29]), "r"(r[OFF + 30]), "r"(r[OFF + 31])
       : "memory");
+}
+// 16 lanes x 256 bits per repetition (8 fp32 columns). Thread t of the warp holds, for column
+// group g (8 columns each): r[4g+0..1] = lane (t/4), columns 8g + 2(t%4) + {0,1};
+// r[4g+2..3] = lane (t/4) + 8, same columns. Four threads (a quad) share a lane.
+__device__ __forceinline__ void tmem_ld_16x256b_x16(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_16x256b_x16(uint32_t taddr, const uint32_t (&r)[64]) {
+  asm volatile("tcgen05.st.sync.aligned.16x256b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63, %64};"
+               :
+               : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(r[32]), "r"(r[33]), "r"(r[34]), "r"(r[35]), "r"(r[36]), "r"(r[37]), "r"(r[38]), "r"(r[39]), "r"(r[40]), "r"(r[41]), "r"(r[42]), "r"(r[43]), "r"(r[44]), "r"(r[45]), "r"(r[46]), "r"(r[47]), "r"(r[48]), "r"(r[49]), "r"(r[50]), "r"(r[51]), "r"(r[52]), "r"(r[53]), "r"(r[54]), "r"(r[55]), "r"(r[56]), "r"(r[57]), "r"(r[58]), "r"(r[59]), "r"(r[60]), "r"(r[61]), "r"(r[62]), "r"(r[63])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_16x256b_x8(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.16x256b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+               :
+               : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+               : "memory");
+}
+// 16 lanes x 128 bits per repetition (4 columns): r[2g+0] = lane (t/4), column 4g + (t%4);
+// r[2g+1] = lane (t/4) + 8, same column.
+template <int N>
+__device__ __forceinline__ void tmem_st_16x128b_x16(uint32_t taddr, const uint32_t (&r)[N]) {
+  asm volatile("tcgen05.st.sync.aligned.16x128b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+               :
+               : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+               : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -272,8 +308,10 @@ struct AttnSmem {
   static constexpr int Q_OFF = 0;
   static constexpr int KV_OFF = ATT_NQ * TILE_BYTES;
   static constexpr int BAR_OFF = KV_OFF + ATT_STAGES * TILE_BYTES;
-  static constexpr int NUM_BARS = 2 + 2 * ATT_STAGES + 6 + 1;
-  static constexpr int TOTAL = BAR_OFF + NUM_BARS * 8 + 64;
+  static constexpr int NUM_BARS = 2 + 2 * ATT_STAGES + 6 + 1 + 2;
+  static constexpr int XCH_OFF = BAR_OFF + NUM_BARS * 8 + 64;      // row max / sum exchange
+  static constexpr int XCH_BYTES = ATT_NQ * 2 * ATT_BM * 4;
+  static constexpr int TOTAL = XCH_OFF + XCH_BYTES;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for 1024-byte alignment
 };
 
@@ -314,6 +352,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   constexpr int B_PFULL = B_SFULL + 2;              // [2]
   constexpr int B_ODONE = B_PFULL + 2;              // [2]
   constexpr int B_DRAIN = B_ODONE + 2;              // [1]
+  constexpr int B_XCH = B_DRAIN + 1;                // [2] row-statistics exchange per Q tile
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::BAR_OFF + L::NUM_BARS * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* fills_issued = reinterpret_cast<int*>(tmem_holder + 2);  // [STAGES]
@@ -356,8 +395,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar(B_SFULL + t), 1);
-      mbar_init(bar(B_PFULL + t), ATT_BM / 32);  // one arrival per softmax warp
+      mbar_init(bar(B_PFULL + t), ATT_SM_WARPS / ATT_NQ);  // one arrival per softmax warp
       mbar_init(bar(B_ODONE + t), 1);
+      mbar_init(bar(B_XCH + t), ATT_SM_WARPS / ATT_NQ);
     }
     mbar_init(bar(B_DRAIN), 1);
     *abort_flag = 0;
@@ -376,7 +416,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 8) {
+  if (warp == ATT_SM_WARPS) {
     // =========================== TMA producer =========================================
     if (lane == 0 && JHI > JLO) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_q) : "memory");
@@ -414,7 +454,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == ATT_SM_WARPS + 1) {
     // =========================== MMA issuer ===========================================
     if (lane == 0 && JHI > JLO) {
       const uint32_t idesc_qk = make_idesc(BF16 ? 1 : 0, ATT_BM, ATT_BN, 0, 0);
@@ -518,23 +558,38 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     }
   } else {
     // =========================== softmax groups =======================================
-    const int t = warp >> 2;                 // Q tile of this group
-    const int r = threadIdx.x & (ATT_BM - 1);  // row within the tile == TMEM lane
-    const int row = m0 + t * ATT_BM + r;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_base + t * ATT_BN;
-    const uint32_t o_addr = tmem_base + lane_base + 2 * ATT_BN + t * ATT_BN;
-    const int n_it = rng[t].jhi - rng[t].jlo;
-
-    // visible key range of this row: lo_i <= col <= hi_i
-    int hi_i = p.Sk - 1, lo_i = 0;
-    if (p.causal) hi_i = min(hi_i, row);
-    if (p.win_right >= 0) hi_i = min(hi_i, row + p.win_right);
-    if (p.win_left >= 0) lo_i = max(0, row - p.win_left);
-    // tile-level: rows [row0, row1] of this Q tile
-    const int row0 = m0 + t * ATT_BM;
+    // 8 warps per Q tile. Warp w of the tile owns 16 rows: TMEM lanes 32*(w%4) + 16*(w/4) .. +15,
+    // read with the 16x256b shape, so that each row is spread over the four threads of a quad
+    // (32 of the 128 score columns each) and each thread works on two rows (lane t/4 and
+    // t/4 + 8). Row maxima need two quad shuffles and no traffic between warps; the partial row
+    // sums are only combined in the epilogue. The epilogue itself re-partitions the tile (one
+    // row per thread, half of the head dim) to write 128 contiguous bytes per thread, and gets
+    // the row sums through shared memory once per CTA.
+    constexpr int WPT = ATT_SM_WARPS / ATT_NQ;              // softmax warps per Q tile
+    const int t = warp / WPT;                               // Q tile of this warp
+    const int wq = warp & 3;                                // TMEM lane quarter of this warp
+    const int sub = (warp >> 2) & 1;                        // which 16 lanes of the quarter
+    const int q4 = lane & 3;                                // position in the quad
+    const int rl = wq * 32 + sub * 16 + (lane >> 2);        // first row (second is rl + 8)
+    const int row0 = m0 + t * ATT_BM;                       // first row of the Q tile
     const int row1 = min(p.Sq, row0 + ATT_BM) - 1;
-    int hi_min = p.Sk - 1, lo_max = 0;
+    const uint32_t lane16 = static_cast<uint32_t>(wq * 32 + sub * 16) << 16;
+    const uint32_t s_addr = tmem_base + lane16 + t * ATT_BN;
+    const uint32_t o_addr16 = tmem_base + lane16 + 2 * ATT_BN + t * ATT_BN;
+    const int n_it = rng[t].jhi - rng[t].jlo;
+    float* xch = reinterpret_cast<float*>(smem + L::XCH_OFF) + t * 2 * ATT_BM;  // [2][128]
+
+    int row_g[2], hi_i[2], lo_i[2];  // global row and its visible key range lo <= col <= hi
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+      row_g[hr] = row0 + rl + 8 * hr;
+      hi_i[hr] = p.Sk - 1;
+      lo_i[hr] = 0;
+      if (p.causal) hi_i[hr] = min(hi_i[hr], row_g[hr]);
+      if (p.win_right >= 0) hi_i[hr] = min(hi_i[hr], row_g[hr] + p.win_right);
+      if (p.win_left >= 0) lo_i[hr] = max(0, row_g[hr] - p.win_left);
+    }
+    int hi_min = p.Sk - 1, lo_max = 0;  // tile-level bounds (first / last row of the tile)
     if (p.causal) hi_min = min(hi_min, row0);
     if (p.win_right >= 0) hi_min = min(hi_min, row0 + p.win_right);
     if (p.win_left >= 0) lo_max = max(0, row1 - p.win_left);
@@ -543,44 +598,20 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     const float slope2 = p.slopes ? p.slopes[h] * 1.4426950408889634f : 0.0f;
     const bool has_alibi = p.slopes != nullptr;
 
-    float m_run = -INFINITY;  // reference max (log2 domain) used for exponentiation
-    float l_run = 0.0f;
+    float m_run[2] = {-INFINITY, -INFINITY};  // reference max (log2 domain) per row
+    float l_run[2] = {0.0f, 0.0f};            // this thread's share of the row sums
     bool ok = true;
 
     for (int itn = 0; itn < n_it && ok; ++itn) {
       const int j = rng[t].jlo + itn;
-      const int c0 = j * ATT_BN;
+      const int c0 = j * ATT_BN;  // first key of the tile
       ok = __all_sync(0xffffffffu,
                       mbar_wait(bar(B_SFULL + t), itn & 1, abort_flag, p.status, ATT_ST_SOFTMAX));
       if (!ok) break;
       tc_fence_after();
-#if defined(TRX_ATT_EXPERIMENT) && TRX_ATT_EXPERIMENT == 1
-      // timing experiment: no softmax at all
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_PFULL + t));
-      continue;
-#endif
-      uint32_t sr[ATT_BN];
-      tmem_ld32<0>(s_addr + 0, sr);
-      tmem_ld32<32>(s_addr + 32, sr);
-      tmem_ld32<64>(s_addr + 64, sr);
-      tmem_ld32<96>(s_addr + 96, sr);
+      uint32_t sr[64];  // sr[4g + 2hr + e] = S(row hr, column 8g + 2*q4 + e)
+      tmem_ld_16x256b_x16(s_addr, sr);
       tmem_wait_ld();
-#if defined(TRX_ATT_EXPERIMENT) && TRX_ATT_EXPERIMENT == 2
-      // timing experiment: TMEM load + convert + TMEM store, no max / exp
-#pragma unroll
-      for (int c = 0; c < ATT_BN; c += 2)
-        sr[c / 2] = pack16<BF16>(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
-      tmem_st32<0>(s_addr + 0, sr);
-      tmem_st32<32>(s_addr + 32, sr);
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_PFULL + t));
-      l_run = 1.0f;
-      continue;
-#endif
 
       const bool need_mask = (c0 + ATT_BN - 1 > hi_min) || (c0 < lo_max);
       // ALiBi on a tile that lies entirely on one side of the diagonal is linear in the
@@ -593,88 +624,128 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       }
       // general path: a tile that straddles the diagonal under ALiBi, or a non-positive scale
       const bool general = (has_alibi && alibi_sgn == 0) || !(sl2 > 0.0f);
-      float m_tile = -INFINITY;
-      float off = 0.0f;  // fast path: x = t * sl2 + off
+      float m_tile[2] = {-INFINITY, -INFINITY};
+      float off[2] = {0.0f, 0.0f};  // fast path: x = t * sl2 + off
       if (general) {
-        const float fi = static_cast<float>(row - c0);
 #pragma unroll
-        for (int c = 0; c < ATT_BN; ++c) {
-          float x = __uint_as_float(sr[c]) * sl2;
-          if (has_alibi) x = fmaf(-slope2, fabsf(fi - static_cast<float>(c)), x);
-          if (need_mask) {
-            const int col = c0 + c;
-            if (col < lo_i || col > hi_i) x = -INFINITY;
+        for (int hr = 0; hr < 2; ++hr) {
+          const float fi = static_cast<float>(row_g[hr] - c0 - 2 * q4);
+#pragma unroll
+          for (int g = 0; g < 16; ++g) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int i = 4 * g + 2 * hr + e;
+              float x = __uint_as_float(sr[i]) * sl2;
+              if (has_alibi) x = fmaf(-slope2, fabsf(fi - static_cast<float>(8 * g + e)), x);
+              if (need_mask) {
+                const int col = c0 + 8 * g + 2 * q4 + e;
+                if (col < lo_i[hr] || col > hi_i[hr]) x = -INFINITY;
+              }
+              sr[i] = __float_as_uint(x);
+              m_tile[hr] = fmaxf(m_tile[hr], x);
+            }
           }
-          sr[c] = __float_as_uint(x);
-          m_tile = fmaxf(m_tile, x);
         }
       } else {
         if (need_mask) {
-          // boundary tile: hide keys outside [lo_i, hi_i] in the raw domain (sl2 > 0 keeps
-          // -inf at -inf), then continue on the fast path
-          const int lo_c = lo_i - c0, hi_c = hi_i - c0;
+          // boundary tile: hide keys outside [lo, hi] in the raw domain (sl2 > 0 keeps -inf
+          // at -inf), then continue on the fast path
 #pragma unroll
-          for (int c = 0; c < ATT_BN; ++c)
-            if (c < lo_c || c > hi_c) sr[c] = 0xff800000u;  // -inf
+          for (int hr = 0; hr < 2; ++hr) {
+            const int lo_c = lo_i[hr] - c0 - 2 * q4, hi_c = hi_i[hr] - c0 - 2 * q4;
+#pragma unroll
+            for (int g = 0; g < 16; ++g) {
+#pragma unroll
+              for (int e = 0; e < 2; ++e)
+                if (8 * g + e < lo_c || 8 * g + e > hi_c) sr[4 * g + 2 * hr + e] = 0xff800000u;
+            }
+          }
         }
         if (alibi_sgn != 0) {
           const float sk = static_cast<float>(alibi_sgn) * slope2;
           const float kc = __fdividef(sk, sl2);
-          off = sk * static_cast<float>(c0 - row);
 #pragma unroll
-          for (int c = 0; c < ATT_BN; ++c)
-            sr[c] = __float_as_uint(fmaf(kc, static_cast<float>(c), __uint_as_float(sr[c])));
-        }
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+          for (int hr = 0; hr < 2; ++hr)
+            off[hr] = sk * static_cast<float>(c0 + 2 * q4 - row_g[hr]);
 #pragma unroll
-        for (int c = 0; c < ATT_BN; c += 8) {
-          mx0 = max3(mx0, __uint_as_float(sr[c + 0]), __uint_as_float(sr[c + 1]));
-          mx1 = max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
-          mx2 = max3(mx2, __uint_as_float(sr[c + 4]), __uint_as_float(sr[c + 5]));
-          mx3 = max3(mx3, __uint_as_float(sr[c + 6]), __uint_as_float(sr[c + 7]));
+          for (int g = 0; g < 16; ++g) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              sr[4 * g + k] = __float_as_uint(
+                  fmaf(kc, static_cast<float>(8 * g + (k & 1)), __uint_as_float(sr[4 * g + k])));
+          }
         }
-        const float mraw = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        m_tile = (mraw == -INFINITY) ? -INFINITY : fmaf(mraw, sl2, off);
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+          float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+          for (int g = 0; g < 16; g += 2) {
+            mx0 = max3(mx0, __uint_as_float(sr[4 * g + 2 * hr]), __uint_as_float(sr[4 * g + 2 * hr + 1]));
+            mx1 = max3(mx1, __uint_as_float(sr[4 * g + 4 + 2 * hr]),
+                       __uint_as_float(sr[4 * g + 5 + 2 * hr]));
+          }
+          const float mraw = fmaxf(mx0, mx1);
+          m_tile[hr] = (mraw == -INFINITY) ? -INFINITY : fmaf(mraw, sl2, off[hr]);
+        }
+      }
+      // the four threads of a quad hold the four column slices of the same two rows
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr) {
+        m_tile[hr] = fmaxf(m_tile[hr], __shfl_xor_sync(0xffffffffu, m_tile[hr], 1));
+        m_tile[hr] = fmaxf(m_tile[hr], __shfl_xor_sync(0xffffffffu, m_tile[hr], 2));
       }
 
       // lazy rescale: keep the old reference max unless the new one is much larger
-      float factor = 1.0f;
+      float factor[2] = {1.0f, 1.0f};
       bool rescale = false;
-      if (m_tile > m_run + ATT_LAZY_RESCALE || (m_run == -INFINITY && m_tile > -INFINITY)) {
-        factor = fast_exp2(m_run - m_tile);  // 0 when m_run == -inf
-        rescale = (itn > 0);
-        m_run = m_tile;
-        l_run *= factor;
+      float m_ref[2];
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr) {
+        if (m_tile[hr] > m_run[hr] + ATT_LAZY_RESCALE ||
+            (m_run[hr] == -INFINITY && m_tile[hr] > -INFINITY)) {
+          factor[hr] = fast_exp2(m_run[hr] - m_tile[hr]);  // 0 when m_run == -inf
+          rescale = rescale || (itn > 0);
+          m_run[hr] = m_tile[hr];
+          l_run[hr] *= factor[hr];
+        }
+        m_ref[hr] = (m_run[hr] == -INFINITY) ? 0.0f : m_run[hr];
       }
-      const float m_ref = (m_run == -INFINITY) ? 0.0f : m_run;
 
-      // P = exp2(x - m_ref), packed to 16-bit pairs in place (sr[0..63])
-      float2 lsum = make_float2(0.0f, 0.0f);
+      // P = exp2(x - m_ref), packed to 16-bit pairs IN PLACE: sr[2g + hr] = P(row hr, column
+      // 4g + q4). Slot 2g + hr never lies ahead of the scores still to be read (4g + 2hr ..).
+      float2 lsum[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
       if (general) {
 #pragma unroll
-        for (int c = 0; c < ATT_BN; c += 2) {
-          const float p0 = fast_exp2(__uint_as_float(sr[c]) - m_ref);
-          const float p1 = fast_exp2(__uint_as_float(sr[c + 1]) - m_ref);
-          lsum.x += p0;
-          lsum.y += p1;
-          sr[c / 2] = pack16<BF16>(p0, p1);
+        for (int g = 0; g < 16; ++g) {
+#pragma unroll
+          for (int hr = 0; hr < 2; ++hr) {
+            const float p0 = fast_exp2(__uint_as_float(sr[4 * g + 2 * hr]) - m_ref[hr]);
+            const float p1 = fast_exp2(__uint_as_float(sr[4 * g + 2 * hr + 1]) - m_ref[hr]);
+            lsum[hr].x += p0;
+            lsum[hr].y += p1;
+            sr[2 * g + hr] = pack16<BF16>(p0, p1);
+          }
         }
       } else {
         const float2 sc2 = make_float2(sl2, sl2);
-        const float2 nm2 = make_float2(off - m_ref, off - m_ref);
+        const float2 nm2[2] = {make_float2(off[0] - m_ref[0], off[0] - m_ref[0]),
+                               make_float2(off[1] - m_ref[1], off[1] - m_ref[1])};
 #pragma unroll
-        for (int c = 0; c < ATT_BN; c += 2) {
-          const float2 x =
-              fma2(make_float2(__uint_as_float(sr[c]), __uint_as_float(sr[c + 1])), sc2, nm2);
-          const float2 pe = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-          lsum = add2(lsum, pe);
-          sr[c / 2] = pack16<BF16>(pe.x, pe.y);
+        for (int g = 0; g < 16; ++g) {
+#pragma unroll
+          for (int hr = 0; hr < 2; ++hr) {
+            const float2 x = fma2(make_float2(__uint_as_float(sr[4 * g + 2 * hr]),
+                                              __uint_as_float(sr[4 * g + 2 * hr + 1])),
+                                  sc2, nm2[hr]);
+            const float2 pe = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+            lsum[hr] = add2(lsum[hr], pe);
+            sr[2 * g + hr] = pack16<BF16>(pe.x, pe.y);
+          }
         }
       }
-      l_run += lsum.x + lsum.y;
-
-      tmem_st32<0>(s_addr + 0, sr);
-      tmem_st32<32>(s_addr + 32, sr);
+      l_run[0] += lsum[0].x + lsum[0].y;
+      l_run[1] += lsum[1].x + lsum[1].y;
+      tmem_st_16x128b_x16(s_addr, sr);
 
       // O rescale (rare after the first tiles): needs the previous PV of this tile done
       if (__any_sync(0xffffffffu, rescale)) {
@@ -682,16 +753,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                                                p.status, ATT_ST_SOFTMAX));
         if (ok) {
           tc_fence_after();
+          uint32_t orr[D / 2];  // same fragment layout as the scores
+          if constexpr (D == 128) tmem_ld_16x256b_x16(o_addr16, orr);
+          else tmem_ld_16x256b_x8(o_addr16, orr);
+          tmem_wait_ld();
 #pragma unroll
-          for (int cc = 0; cc < D; cc += 32) {
-            uint32_t orr[32];
-            tmem_ld32<0>(o_addr + cc, orr);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; ++e)
-              orr[e] = __float_as_uint(__uint_as_float(orr[e]) * factor);
-            tmem_st32<0>(o_addr + cc, orr);
-          }
+          for (int i = 0; i < D / 2; ++i)
+            orr[i] = __float_as_uint(__uint_as_float(orr[i]) * factor[(i >> 1) & 1]);
+          if constexpr (D == 128) tmem_st_16x256b_x16(o_addr16, orr);
+          else tmem_st_16x256b_x8(o_addr16, orr);
         }
       }
       tmem_wait_st();
@@ -701,18 +771,43 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     }
 
     // ---- epilogue: O / l -> global --------------------------------------------------
+    // Row statistics go through shared memory once: xch[0][row] = row sum, xch[1][row] = max.
+    if (ok) {
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr) {
+        float l = l_run[hr];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (q4 == 0) {
+          xch[rl + 8 * hr] = l;
+          xch[ATT_BM + rl + 8 * hr] = m_run[hr];
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_XCH + t));
+      ok = __all_sync(0xffffffffu,
+                      mbar_wait(bar(B_XCH + t), 0, abort_flag, p.status, ATT_ST_SOFTMAX));
+    }
     if (ok && n_it > 0) {
       ok = __all_sync(0xffffffffu, mbar_wait(bar(B_ODONE + t), (n_it - 1) & 1, abort_flag,
                                              p.status, ATT_ST_SOFTMAX));
       tc_fence_after();
     }
     if (ok) {
-      const float inv = (n_it > 0 && l_run > 0.0f) ? __fdividef(1.0f, l_run) : 0.0f;
+      // one row per thread (TMEM lane 32*wq + lane), columns [OC*sub, OC*sub + OC) of the head
+      constexpr int OC = D / 2;
+      const int r = wq * 32 + lane;
+      const int row = row0 + r;
+      const float l_row = xch[r];
+      const float m_row = xch[ATT_BM + r];
+      const float inv = (n_it > 0 && l_row > 0.0f) ? __fdividef(1.0f, l_row) : 0.0f;
+      const uint32_t o_addr = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + 2 * ATT_BN +
+                              t * ATT_BN + sub * OC;
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
                       2ll * (b * p.o_stride_b + static_cast<long long>(row) * p.o_stride_s +
-                             h * p.o_stride_h);
+                             h * p.o_stride_h + sub * OC);
 #pragma unroll
-      for (int cc = 0; cc < D; cc += 32) {
+      for (int cc = 0; cc < OC; cc += 32) {
         uint32_t orr[32];
         if (n_it > 0) {
           tmem_ld32<0>(o_addr + cc, orr);  // warp-collective: executed by every lane
@@ -736,9 +831,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
           }
         }
       }
-      if (p.lse && row < p.Sq) {
-        const float lse = (n_it > 0 && l_run > 0.0f)
-                              ? (m_run + log2f(l_run)) * 0.6931471805599453f
+      if (p.lse && sub == 0 && row < p.Sq) {
+        const float lse = (n_it > 0 && l_row > 0.0f)
+                              ? (m_row + log2f(l_row)) * 0.6931471805599453f
                               : -INFINITY;
         p.lse[b * p.lse_stride_b + h * p.lse_stride_h + row] = lse;
       }
