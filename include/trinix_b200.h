@@ -107,6 +107,32 @@ int trx_rmsnorm_quant_i8(const void* x, const void* w, int8_t* codes, float* sca
                          int x_dtype, int w_dtype, void* stream);
 
 /*
+ * Fused residual add + RMSNorm: s = float(x) + float(residual) (kept in fp32 on chip),
+ *   y = round_x(w * round_x(s * rstd(s))); `sum_out_or_null` receives round_x(s), the new
+ *   residual stream, when non-NULL.
+ * Follows FastFusedResidualRMSNorm._pytorch_forward, trinix/layers/fused/residual_rmsnorm.py:66-73.
+ * Replaces TritonFusedResidualRMSNormFunction.forward,
+ * trinix/kernels/fused/residual_rmsnorm_kernel.py:212-248 (kernel :9-73), reached through
+ * TritonFusedResidualRMSNormKernel.apply(X, Residual, W, eps).
+ */
+int trx_residual_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y,
+                             void* sum_out_or_null, float* rstd_or_null, int64_t R, int64_t C,
+                             int64_t x_row_stride, int64_t res_row_stride, int64_t y_row_stride,
+                             int64_t sum_row_stride, float eps, int x_dtype, int w_dtype,
+                             void* stream);
+
+/*
+ * Fused residual add + RMSNorm -> int8: quantises exactly the rows trx_residual_rmsnorm_fwd
+ * would write, without writing them; optionally writes the summed residual stream.
+ * No counterpart in the reference (it has no int8 code).
+ */
+int trx_residual_rmsnorm_quant_i8(const void* x, const void* residual, const void* w, int8_t* codes,
+                                  float* scales, void* sum_out_or_null, int64_t R, int64_t C,
+                                  int64_t x_row_stride, int64_t res_row_stride,
+                                  int64_t codes_row_stride, int64_t sum_row_stride, float eps,
+                                  int x_dtype, int w_dtype, void* stream);
+
+/*
  * Rotary position embedding, half-split ("rotate_half") form, q and k in one launch:
  *   o[..., :D/2] = x1*cos - x2*sin ;  o[..., D/2:] = x2*cos + x1*sin
  * with cos/sin rows indexed by the sequence position (tables are (S, >= D/2),

@@ -26,6 +26,7 @@ from trinix.layers.embeddings.alibi import FastALiBiPositionEmbedding  # noqa: E
 from trinix.layers.embeddings.rope import FastRoPEPositionEmbedding  # noqa: E402
 from trinix.layers.norm.layernorm import FastLayerNorm  # noqa: E402
 from trinix.layers.norm.rmsnorm import FastRMSNorm  # noqa: E402
+from trinix.layers.fused.residual_rmsnorm import FastFusedResidualRMSNorm  # noqa: E402
 
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz")
 vec = {}
@@ -67,6 +68,14 @@ with torch.no_grad():
     xlb = torch.randn(16, 320, generator=g).bfloat16()
     mlb = FastLayerNorm(320, elementwise_affine=False, use_triton=False)
     put("ln_bf16_x", xlb); put("ln_bf16_y", mlb(xlb))
+
+    # --- fused residual + RMSNorm, bf16 (sum formed in fp32)
+    xr = torch.randn(10, 512, generator=g).bfloat16()
+    rr = torch.randn(10, 512, generator=g).bfloat16()
+    wr = (1 + 0.05 * torch.randn(512, generator=g)).bfloat16()
+    mr = FastFusedResidualRMSNorm(512, eps=1e-6, use_triton=False).bfloat16()
+    mr.weight.copy_(wr)
+    put("resrms_x", xr); put("resrms_r", rr); put("resrms_w", wr); put("resrms_y", mr(xr, rr))
 
     # --- RoPE: fp32 tables (built from an fp32 dummy) and bf16 tables (built from q)
     rope = FastRoPEPositionEmbedding(64, 2048, 10000.0, use_triton=False)

@@ -174,3 +174,39 @@ def test_quantize_full_size_properties(cuda):
     c2, s2 = T.quantize_rowwise(deq)
     assert torch.equal(c2, codes)
     assert torch.equal(T.quantize_rowwise(y)[0], codes)
+
+
+def test_residual_rmsnorm_golden_and_shapes(cuda):
+    x, r, w = G("resrms_x"), G("resrms_r"), G("resrms_w")
+    y = T.TritonFusedResidualRMSNormKernel.apply(x.to(cuda), r.to(cuda), w.to(cuda), 1e-6)
+    assert int(bf16_ulps(y.cpu(), G("resrms_y")).max()) <= 1
+    g = torch.Generator().manual_seed(11)
+    for rows, cols, dtype in [(64, 4096, torch.bfloat16), (5, 8192, torch.bfloat16),
+                              (3, 777, torch.bfloat16), (4, 4104, torch.float32),
+                              (2, 40000, torch.float16), (3, 520, torch.float16)]:
+        x = torch.randn(rows, cols, generator=g).to(dtype)
+        r = (torch.randn(rows, cols, generator=g) * 3).to(dtype)
+        w = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype)
+        y, s = T.ops.residual_rmsnorm(x.to(cuda), r.to(cuda), w.to(cuda), 1e-6, return_sum=True)
+        ref = R.residual_rmsnorm_ref(x, r, w, 1e-6)
+        assert rel_err(y.cpu(), ref) <= (1e-5 if dtype == torch.float32 else 1e-2)
+        # the summed residual stream is the fp32 sum rounded once to the activation dtype
+        assert torch.equal(s.cpu(), (x.float() + r.float()).to(dtype))
+        if dtype == torch.bfloat16:
+            d = bf16_ulps(y.cpu(), ref)
+            assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 2e-3
+
+
+def test_residual_rmsnorm_quant_equals_unfused_bit_exact(cuda):
+    g = torch.Generator().manual_seed(12)
+    for rows, cols, dtype in [(512, 4096, torch.bfloat16), (7, 1000, torch.bfloat16),
+                              (3, 8192, torch.float32), (5, 12288, torch.float16)]:
+        x = torch.randn(rows, cols, generator=g).to(dtype).to(cuda)
+        r = torch.randn(rows, cols, generator=g).to(dtype).to(cuda)
+        w = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype).to(cuda)
+        codes, scales, s = T.residual_rmsnorm_quantize(x, r, w, 1e-6, return_sum=True)
+        y, s2 = T.ops.residual_rmsnorm(x, r, w, 1e-6, return_sum=True)
+        c2, sc2 = T.quantize_rowwise(y)
+        assert torch.equal(codes, c2) and torch.equal(scales.view(torch.int32), sc2.view(torch.int32))
+        assert torch.equal(s, s2)
+        _assert_quant_exact(y.cpu(), codes, scales)  # oracle quantiser on the kernel's norm output

@@ -47,6 +47,9 @@ def test_mirror_modules_take_torch_path_on_cpu_and_match_oracle():
         ln = T.FastLayerNorm(768, eps=1e-5)
         ln.weight.copy_(G("ln_f32_w")); ln.bias.copy_(G("ln_f32_b"))
         torch.testing.assert_close(ln(G("ln_f32_x")), G("ln_f32_y"), rtol=2e-6, atol=2e-6)
+        fr = T.FastFusedResidualRMSNorm(512, eps=1e-6).bfloat16()
+        fr.weight.copy_(G("resrms_w"))
+        assert torch.equal(fr(G("resrms_x"), G("resrms_r")), G("resrms_y"))
         for name, cls in (("swiglu", T.FastSwiGLU), ("geglu", T.FastGeGLU), ("reglu", T.FastReGLU)):
             torch.testing.assert_close(cls(96)(G(f"{name}_f32_x")), G(f"{name}_f32_y"),
                                        rtol=2e-6, atol=2e-6)

@@ -30,6 +30,12 @@ def test_rmsnorm_fp32_weight_promotes():
     assert y.dtype == torch.float32  # reference behaviour: weight * x.to(input_dtype)
 
 
+def test_residual_rmsnorm():
+    y = R.residual_rmsnorm_ref(G("resrms_x"), G("resrms_r"), G("resrms_w"), 1e-6)
+    assert y.dtype == torch.bfloat16
+    assert int(bf16_ulps(y, G("resrms_y")).max()) <= 1
+
+
 def test_layernorm():
     y = R.layernorm_ref(G("ln_f32_x"), G("ln_f32_w"), G("ln_f32_b"), 1e-5)
     torch.testing.assert_close(y, G("ln_f32_y"), **F32_TOL)

@@ -10,6 +10,7 @@ from .install import install, uninstall
 from .kernels import (
     RowwiseInt8Kernel,
     TritonAttentionKernel,
+    TritonFusedResidualRMSNormKernel,
     TritonGeGLUKernel,
     TritonLayerNormKernel,
     TritonReGLUKernel,
@@ -20,6 +21,7 @@ from .kernels import (
 from .layers import (
     FastALiBiPositionEmbedding,
     FastBaseAttention,
+    FastFusedResidualRMSNorm,
     FastGeGLU,
     FastGroupedQueryAttention,
     FastLayerNorm,
@@ -37,6 +39,8 @@ from .ops import (
     glu_pair,
     layernorm,
     quantize_rowwise,
+    residual_rmsnorm,
+    residual_rmsnorm_quantize,
     rmsnorm,
     rmsnorm_quantize,
     rope,

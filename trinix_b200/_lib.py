@@ -32,6 +32,12 @@ SIGNATURES = {
                                        c_int64, c_int, c_void_p]),
     "trx_rmsnorm_quant_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                      c_int64, c_int64, c_float, c_int, c_int, c_void_p]),
+    "trx_residual_rmsnorm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                         c_float, c_int, c_int, c_void_p]),
+    "trx_residual_rmsnorm_quant_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                              c_int64, c_int64, c_float, c_int, c_int, c_void_p]),
     "trx_rope_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                              c_int64, c_int64, c_int64, c_int64, I64x3, I64x3, I64x3, I64x3,
                              c_int64, c_int, c_int, c_int, c_void_p]),

@@ -34,9 +34,24 @@ namespace trx {
 #define TRX_ROW_MINBLOCKS(TPR) ((TPR) > 32 ? ((TPR) <= 256 ? 1024 / (TPR) : 1) : 3)
 #endif
 
-enum RowOp { OP_RMSNORM = 0, OP_LAYERNORM = 1, OP_QUANT = 2, OP_RMSNORM_QUANT = 3 };
+enum RowOp {
+  OP_RMSNORM = 0,
+  OP_LAYERNORM = 1,
+  OP_QUANT = 2,
+  OP_RMSNORM_QUANT = 3,
+  OP_RES_RMSNORM = 4,        // RMSNorm(x + residual)
+  OP_RES_RMSNORM_QUANT = 5   // RMSNorm(x + residual) -> int8
+};
+__host__ __device__ constexpr bool op_is_rms(int op) {
+  return op == OP_RMSNORM || op == OP_RMSNORM_QUANT || op == OP_RES_RMSNORM ||
+         op == OP_RES_RMSNORM_QUANT;
+}
+__host__ __device__ constexpr bool op_has_quant(int op) {
+  return op == OP_QUANT || op == OP_RMSNORM_QUANT || op == OP_RES_RMSNORM_QUANT;
+}
+__host__ __device__ constexpr bool op_has_res(int op) { return op == OP_RES_RMSNORM || op == OP_RES_RMSNORM_QUANT; }
 
-struct RowParams {
+struct RowParamsBase {
   const void* x;
   const void* w;
   const void* b;
@@ -53,6 +68,25 @@ struct RowParams {
   float eps;
   int w_dtype;
 };
+// What the residual variants take on top, as a second kernel argument: a parameter block above
+// 128 bytes is no longer read field by field, which cost the plain kernels 5-9 %.
+struct ResParams {
+  const void* res;     // residual added to x before RMSNorm (fp32 sum)
+  void* sum_out;       // optional: round_T(x + res)
+  int64_t res_stride;  // elements
+  int64_t sum_stride;  // elements
+};
+struct NoRes {};
+struct RowParams : RowParamsBase {
+  ResParams rp;
+};
+template <int OP>
+using ResArg = std::conditional_t<op_has_res(OP), ResParams, NoRes>;
+template <int OP>
+static ResArg<OP> res_arg(const RowParams& p) {
+  if constexpr (op_has_res(OP)) return p.rp;
+  else return NoRes{};
+}
 
 // Packed product of two 16-bit pairs with one rounding per lane.
 template <typename T>
@@ -74,14 +108,18 @@ __device__ __forceinline__ uint32_t mul_packed16<float>(uint32_t a, uint32_t) {
 }
 
 template <int OP, typename T, int TPR, int VPT>
-__global__ void __launch_bounds__((TPR > 32 ? TPR : 256), TRX_ROW_MINBLOCKS(TPR))
-    row_kernel(const RowParams p) {
+__global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
+                                  (op_has_res(OP) && TPR > 32 && TPR <= 256) ? 768 / TPR
+                                                                               : TRX_ROW_MINBLOCKS(TPR))
+    row_kernel(const RowParamsBase p, const ResArg<OP> rp) {
   using P = Pack<T>;
   constexpr int VEC = P::VEC;
   constexpr int BLOCK = TPR > 32 ? TPR : 256;
   constexpr int ROWS_PER_CTA = BLOCK / TPR;
-  constexpr bool HAS_NORM = (OP == OP_RMSNORM || OP == OP_LAYERNORM || OP == OP_RMSNORM_QUANT);
-  constexpr bool HAS_QUANT = (OP == OP_QUANT || OP == OP_RMSNORM_QUANT);
+  constexpr bool HAS_NORM = op_is_rms(OP) || OP == OP_LAYERNORM;
+  constexpr bool HAS_QUANT = op_has_quant(OP);
+  constexpr bool HAS_RES = op_has_res(OP);
+  constexpr bool NORM_TO_REGS = (OP == OP_RMSNORM_QUANT || OP == OP_RES_RMSNORM_QUANT);
 
   __shared__ __align__(16) float red[2][32];
   int sel = 0;
@@ -93,7 +131,7 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), TRX_ROW_MINBLOCKS(TPR)
   const int64_t row_step = static_cast<int64_t>(gridDim.x) * ROWS_PER_CTA;
   // fp32 copies of the row are kept between the statistics and the normalise pass when they
   // fit (saves re-unpacking); longer per-thread slices unpack twice instead.
-  constexpr bool KEEP_F32 = (VEC == 8) && (VPT <= 4) && (OP == OP_RMSNORM || OP == OP_RMSNORM_QUANT);
+  constexpr bool KEEP_F32 = (VEC == 8) && (VPT <= 4) && HAS_NORM;
 
   for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * ROWS_PER_CTA; row0 < p.R;
        row0 += row_step) {
@@ -116,12 +154,36 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), TRX_ROW_MINBLOCKS(TPR)
 
     float mean = 0.0f, rstd = 1.0f;
     // ---- 2. statistics -------------------------------------------------------------
-    if constexpr (OP == OP_RMSNORM || OP == OP_RMSNORM_QUANT) {
+    if constexpr (op_is_rms(OP)) {
       float2 ss2 = make_float2(0.0f, 0.0f);
+      // residual variants: the host guarantees a configuration that keeps fp32 copies
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         float2 f2[VEC / 2];
         P::unpack2(raw[i], f2);
+        if constexpr (HAS_RES) {
+          const T* rrow = reinterpret_cast<const T*>(rp.res) + (row_ok ? row : 0) * rp.res_stride;
+          T* srow = reinterpret_cast<T*>(rp.sum_out) + (row_ok ? row : 0) * rp.sum_stride;
+          // residual stream: the sum is formed and normalised in fp32, as the reference's
+          // PyTorch path does (layers/fused/residual_rmsnorm.py:66-73)
+          const int v = i * TPR + t;
+          if (row_ok && v < nvec) {
+            const int64_t col = static_cast<int64_t>(v) * VEC;
+            float2 r2[VEC / 2];
+            P::unpack2(ld_stream16(rrow + col), r2);
+#pragma unroll
+            for (int j = 0; j < VEC / 2; ++j) f2[j] = add2(f2[j], r2[j]);
+            if constexpr (VEC == 4) {
+              raw[i] = make_uint4(__float_as_uint(f2[0].x), __float_as_uint(f2[0].y),
+                                  __float_as_uint(f2[1].x), __float_as_uint(f2[1].y));
+              if (rp.sum_out) st_stream16(srow + col, raw[i]);
+            } else {
+              if (rp.sum_out)
+                st_stream16(srow + col, make_uint4(P::pack2(f2[0].x, f2[0].y), P::pack2(f2[1].x, f2[1].y),
+                                                   P::pack2(f2[2].x, f2[2].y), P::pack2(f2[3].x, f2[3].y)));
+            }
+          }
+        }
 #pragma unroll
         for (int j = 0; j < VEC / 2; ++j) {
           ss2 = fma2(f2[j], f2[j], ss2);
@@ -132,30 +194,40 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), TRX_ROW_MINBLOCKS(TPR)
       const float var = __fdiv_rn(ss, static_cast<float>(p.C));
       rstd = __fdiv_rn(1.0f, __fsqrt_rn(var + p.eps));
     } else if constexpr (OP == OP_LAYERNORM) {
-      float s = 0.0f;
+      float2 s2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
-        float f[VEC];
-        P::unpack(raw[i], f);
+        float2 f2[VEC / 2];
+        P::unpack2(raw[i], f2);
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) s += f[j];
+        for (int j = 0; j < VEC / 2; ++j) {
+          s2 = add2(s2, f2[j]);
+          if constexpr (KEEP_F32) xf[i][j] = f2[j];
+        }
       }
-      s = row_reduce<TPR, false>(s, red, sel);
+      const float s = row_reduce<TPR, false>(s2.x + s2.y, red, sel);
       mean = __fdiv_rn(s, static_cast<float>(p.C));
-      float cs = 0.0f;
+      const float2 nmean2 = make_float2(-mean, -mean);
+      float2 cs2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int v = i * TPR + t;
-        if (v < nvec) {
-          float f[VEC];
-          P::unpack(raw[i], f);
+        if (v < nvec) {  // padding vectors must not contribute (0 - mean)^2
+          float2 f2[VEC / 2];
+          if constexpr (KEEP_F32) {
 #pragma unroll
-          for (int j = 0; j < VEC; ++j) {
-            const float d = f[j] - mean;
-            cs = fmaf(d, d, cs);
+            for (int j = 0; j < VEC / 2; ++j) f2[j] = xf[i][j];
+          } else {
+            P::unpack2(raw[i], f2);
+          }
+#pragma unroll
+          for (int j = 0; j < VEC / 2; ++j) {
+            const float2 d = add2(f2[j], nmean2);
+            cs2 = fma2(d, d, cs2);
           }
         }
       }
+      float cs = cs2.x + cs2.y;
       cs = row_reduce<TPR, false>(cs, red, sel);
       const float var = __fdiv_rn(cs, static_cast<float>(p.C));
       rstd = __fdiv_rn(1.0f, __fsqrt_rn(var + p.eps));
@@ -170,11 +242,11 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), TRX_ROW_MINBLOCKS(TPR)
     // ---- 3. normalise (registers -> registers, or registers -> HBM) ----------------
     // All dtype / null-pointer decisions are taken once per row, outside the vector loops.
     if constexpr (HAS_NORM) {
-      T* yrow = (OP == OP_RMSNORM_QUANT)
+      T* yrow = NORM_TO_REGS
                     ? nullptr
                     : reinterpret_cast<T*>(p.y) + (row_ok ? row : 0) * p.y_stride;
       auto emit = [&](int i, int64_t col, const uint4& packed) {
-        if constexpr (OP == OP_RMSNORM_QUANT) {
+        if constexpr (NORM_TO_REGS) {
           raw[i] = packed;
         } else {
           st_stream16(yrow + col, packed);
@@ -186,7 +258,15 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), TRX_ROW_MINBLOCKS(TPR)
           const int v = i * TPR + t;
           if (row_ok && v < nvec) {
             float f[VEC];
-            P::unpack(raw[i], f);
+            if constexpr (KEEP_F32) {
+#pragma unroll
+              for (int j = 0; j < VEC / 2; ++j) {
+                f[2 * j] = xf[i][j].x;
+                f[2 * j + 1] = xf[i][j].y;
+              }
+            } else {
+              P::unpack(raw[i], f);
+            }
             const int64_t col = static_cast<int64_t>(v) * VEC;
             float wv[VEC], bv[VEC];
             if (p.w) load_param_vec<VEC>(p.w, p.w_dtype, col, wv);
@@ -299,19 +379,30 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), TRX_ROW_MINBLOCKS(TPR)
 // Scalar multi-pass fallback: one CTA per row, any C, any alignment. The row is
 // re-read from global memory (L2-resident after the first pass).
 template <int OP, typename T>
-__global__ void __launch_bounds__(256) row_kernel_generic(const RowParams p) {
+__global__ void __launch_bounds__(256) row_kernel_generic(const RowParamsBase p, const ResArg<OP> rp) {
   using P = Pack<T>;
   __shared__ __align__(16) float red[2][32];
   int sel = 0;
-  constexpr bool HAS_QUANT = (OP == OP_QUANT || OP == OP_RMSNORM_QUANT);
+  constexpr bool HAS_QUANT = op_has_quant(OP);
   for (int64_t row = blockIdx.x; row < p.R; row += gridDim.x) {
     const T* xrow = reinterpret_cast<const T*>(p.x) + row * p.x_stride;
     float mean = 0.0f, rstd = 1.0f;
-    if constexpr (OP == OP_RMSNORM || OP == OP_RMSNORM_QUANT) {
+    const T* rrow = nullptr;
+    T* srow = nullptr;
+    if constexpr (op_has_res(OP)) {
+      rrow = reinterpret_cast<const T*>(rp.res) + row * rp.res_stride;
+      if (rp.sum_out) srow = reinterpret_cast<T*>(rp.sum_out) + row * rp.sum_stride;
+    }
+    auto xval = [&](int64_t c) -> float {  // x, or the fp32 sum x + residual
+      const float f = P::load1(xrow + c);
+      return rrow ? f + P::load1(rrow + c) : f;
+    };
+    if constexpr (op_is_rms(OP)) {
       float ss = 0.0f;
       for (int64_t c = threadIdx.x; c < p.C; c += 256) {
-        const float f = P::load1(xrow + c);
+        const float f = xval(c);
         ss = fmaf(f, f, ss);
+        if (srow) P::store1(srow + c, f);
       }
       ss = row_reduce<256, false>(ss, red, sel);
       rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(ss, static_cast<float>(p.C)) + p.eps));
@@ -333,7 +424,7 @@ __global__ void __launch_bounds__(256) row_kernel_generic(const RowParams p) {
       if (OP == OP_LAYERNORM && p.mean) p.mean[row] = mean;
     }
     auto normed = [&](int64_t c) -> float {
-      const float f = P::load1(xrow + c);
+      const float f = xval(c);
       if constexpr (OP == OP_LAYERNORM) {
         float o = (f - mean) * rstd;
         if (p.w) o *= load_param1(p.w, p.w_dtype, c);
@@ -394,7 +485,7 @@ static int launch_cfg(const RowParams& p, cudaStream_t stream) {
   const int64_t need = (p.R + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
   const int64_t cap = static_cast<int64_t>(sm_count_of_current_device()) * blocks_per_sm;
   const unsigned grid = static_cast<unsigned>(need < cap ? need : cap);
-  row_kernel<OP, T, TPR, VPT><<<grid, BLOCK, 0, stream>>>(p);
+  row_kernel<OP, T, TPR, VPT><<<grid, BLOCK, 0, stream>>>(static_cast<const RowParamsBase&>(p), res_arg<OP>(p));
   return cudaGetLastError() == cudaSuccess ? TRX_OK : TRX_ERR_CUDA;
 }
 
@@ -402,14 +493,21 @@ template <int OP, typename T>
 static int launch_row(const RowParams& p, cudaStream_t stream) {
   constexpr int VEC = Pack<T>::VEC;
   if (p.R == 0) return TRX_OK;
-  constexpr bool HAS_QUANT = (OP == OP_QUANT || OP == OP_RMSNORM_QUANT);
-  constexpr bool WRITES_Y = (OP == OP_RMSNORM || OP == OP_LAYERNORM);
+  constexpr bool HAS_QUANT = op_has_quant(OP);
+  constexpr bool WRITES_Y = (OP == OP_RMSNORM || OP == OP_LAYERNORM || OP == OP_RES_RMSNORM);
   bool vec_ok = (p.C % VEC == 0) && aligned_to(p.x, 16) && (p.x_stride % VEC == 0);
   if (WRITES_Y) vec_ok = vec_ok && aligned_to(p.y, 16) && (p.y_stride % VEC == 0);
   if (HAS_QUANT) vec_ok = vec_ok && aligned_to(p.codes, VEC) && (p.codes_stride % VEC == 0);
   if (p.w) vec_ok = vec_ok && aligned_to(p.w, 16);
   if (p.b) vec_ok = vec_ok && aligned_to(p.b, 16);
   const int64_t nvec = p.C / VEC;
+  if constexpr (op_has_res(OP)) {
+    vec_ok = vec_ok && aligned_to(p.rp.res, 16) && (p.rp.res_stride % VEC == 0);
+    if (p.rp.sum_out) vec_ok = vec_ok && aligned_to(p.rp.sum_out, 16) && (p.rp.sum_stride % VEC == 0);
+    // the fp32 sum has to stay on chip: fp32 rows hold it in place, 16-bit rows only in the
+    // configurations that keep fp32 copies (at most 4 vectors per thread)
+    if (VEC == 8 && nvec > 4096) vec_ok = false;
+  }
   if (vec_ok && nvec <= 16384) {
     if (nvec <= 32) return launch_cfg<OP, T, 32, 1>(p, stream);
     if (nvec <= 64) return launch_cfg<OP, T, 32, 2>(p, stream);
@@ -424,7 +522,7 @@ static int launch_row(const RowParams& p, cudaStream_t stream) {
   }
   const int64_t cap = static_cast<int64_t>(sm_count_of_current_device()) * 8;
   const unsigned grid = static_cast<unsigned>(p.R < cap ? p.R : cap);
-  row_kernel_generic<OP, T><<<grid, 256, 0, stream>>>(p);
+  row_kernel_generic<OP, T><<<grid, 256, 0, stream>>>(static_cast<const RowParamsBase&>(p), res_arg<OP>(p));
   return cudaGetLastError() == cudaSuccess ? TRX_OK : TRX_ERR_CUDA;
 }
 
@@ -504,4 +602,46 @@ extern "C" int trx_rmsnorm_quant_i8(const void* x, const void* w, int8_t* codes,
   p.R = R; p.C = C; p.x_stride = x_row_stride; p.codes_stride = codes_row_stride;
   p.eps = eps; p.w_dtype = w_dtype;
   return launch_row_dtype<OP_RMSNORM_QUANT>(p, x_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int trx_residual_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y,
+                                        void* sum_out_or_null, float* rstd_or_null, int64_t R,
+                                        int64_t C, int64_t x_row_stride, int64_t res_row_stride,
+                                        int64_t y_row_stride, int64_t sum_row_stride, float eps,
+                                        int x_dtype, int w_dtype, void* stream) {
+  if (!dtype_ok(x_dtype) || !dtype_ok(w_dtype)) return TRX_ERR_DTYPE;
+  if (R < 0 || C <= 0) return TRX_ERR_SHAPE;
+  if (R == 0) return TRX_OK;
+  if (!x || !residual || !w || !y) return TRX_ERR_NULL_POINTER;
+  if (x_row_stride < C || res_row_stride < C || y_row_stride < C ||
+      (sum_out_or_null && sum_row_stride < C))
+    return TRX_ERR_STRIDE;
+  RowParams p{};
+  p.x = x; p.rp.res = residual; p.rp.sum_out = sum_out_or_null; p.w = w; p.y = y; p.rstd = rstd_or_null;
+  p.R = R; p.C = C; p.x_stride = x_row_stride; p.rp.res_stride = res_row_stride;
+  p.y_stride = y_row_stride; p.rp.sum_stride = sum_row_stride;
+  p.eps = eps; p.w_dtype = w_dtype;
+  return launch_row_dtype<OP_RES_RMSNORM>(p, x_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int trx_residual_rmsnorm_quant_i8(const void* x, const void* residual, const void* w,
+                                             int8_t* codes, float* scales, void* sum_out_or_null,
+                                             int64_t R, int64_t C, int64_t x_row_stride,
+                                             int64_t res_row_stride, int64_t codes_row_stride,
+                                             int64_t sum_row_stride, float eps, int x_dtype,
+                                             int w_dtype, void* stream) {
+  if (!dtype_ok(x_dtype) || !dtype_ok(w_dtype)) return TRX_ERR_DTYPE;
+  if (R < 0 || C <= 0) return TRX_ERR_SHAPE;
+  if (R == 0) return TRX_OK;
+  if (!x || !residual || !w || !codes || !scales) return TRX_ERR_NULL_POINTER;
+  if (x_row_stride < C || res_row_stride < C || codes_row_stride < C ||
+      (sum_out_or_null && sum_row_stride < C))
+    return TRX_ERR_STRIDE;
+  RowParams p{};
+  p.x = x; p.rp.res = residual; p.rp.sum_out = sum_out_or_null; p.w = w; p.codes = codes;
+  p.scales = scales;
+  p.R = R; p.C = C; p.x_stride = x_row_stride; p.rp.res_stride = res_row_stride;
+  p.codes_stride = codes_row_stride; p.rp.sum_stride = sum_row_stride;
+  p.eps = eps; p.w_dtype = w_dtype;
+  return launch_row_dtype<OP_RES_RMSNORM_QUANT>(p, x_dtype, static_cast<cudaStream_t>(stream));
 }

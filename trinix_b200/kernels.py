@@ -71,6 +71,19 @@ class TritonLayerNormKernel:
         return _run(lambda x, w, bb: ops.layernorm(x, w, bb, eps), X, W, b)
 
 
+class TritonFusedResidualRMSNormKernel:
+    """Same interface as trinix/kernels/fused/residual_rmsnorm_kernel.py:
+    apply(X, Residual, W, eps) -> RMSNorm(X + Residual)."""
+
+    @staticmethod
+    def is_available() -> bool:
+        return _available()
+
+    @staticmethod
+    def apply(X: torch.Tensor, Residual: torch.Tensor, W: torch.Tensor, eps: float) -> torch.Tensor:
+        return _run(lambda x, r, w: ops.residual_rmsnorm(x, r, w, eps), X, Residual, W)
+
+
 class TritonRoPEKernel:
     """Same interface as trinix/kernels/rope_kernel.py:180-222: (q, k, cos, sin) -> (q', k')."""
 
@@ -169,10 +182,17 @@ class RowwiseInt8Kernel:
     def rmsnorm_quantize(X: torch.Tensor, W: torch.Tensor, eps: float):
         return ops.rmsnorm_quantize(X.detach(), W.detach(), eps)
 
+    @staticmethod
+    def residual_rmsnorm_quantize(X: torch.Tensor, Residual: torch.Tensor, W: torch.Tensor,
+                                  eps: float, return_sum: bool = False):
+        return ops.residual_rmsnorm_quantize(X.detach(), Residual.detach(), W.detach(), eps,
+                                             return_sum)
+
 
 KERNEL_CLASSES = {
     "TritonRMSNormKernel": TritonRMSNormKernel,
     "TritonLayerNormKernel": TritonLayerNormKernel,
+    "TritonFusedResidualRMSNormKernel": TritonFusedResidualRMSNormKernel,
     "TritonRoPEKernel": TritonRoPEKernel,
     "TritonSwiGLUKernel": TritonSwiGLUKernel,
     "TritonGeGLUKernel": TritonGeGLUKernel,

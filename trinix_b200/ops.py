@@ -174,6 +174,55 @@ def rmsnorm_quantize(x: torch.Tensor, weight: torch.Tensor,
     return codes.view(x.shape), scales.view(x.shape[:-1])
 
 
+def residual_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
+                     eps: float = 1e-6, return_sum: bool = False):
+    """RMSNorm(x + residual) with the sum kept in fp32 on chip; optionally also returns the
+    summed residual stream rounded to x's dtype."""
+    dev = _need_cuda(x, residual, weight)
+    if residual.shape != x.shape or residual.dtype != x.dtype:
+        raise ValueError("residual must have the shape and dtype of x")
+    if weight.numel() != x.shape[-1]:
+        raise ValueError(f"weight has {weight.numel()} elements, rows have {x.shape[-1]}")
+    x2, r2 = _rows(x), _rows(residual)
+    w = weight.detach().contiguous()
+    y = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=dev)
+    s = torch.empty_like(y) if return_sum else None
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_residual_rmsnorm_fwd(
+            _ptr(x2), _ptr(r2), _ptr(w), _ptr(y), _ptr(s), None, x2.shape[0], x2.shape[1],
+            _row_stride(x2), _row_stride(r2), x2.shape[1], x2.shape[1], float(eps), _code(x2),
+            _code(w), _stream(dev))
+    _lib.check("trx_residual_rmsnorm_fwd", rc)
+    _count()
+    y = y.view(x.shape)
+    return (y, s.view(x.shape)) if return_sum else y
+
+
+def residual_rmsnorm_quantize(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
+                              eps: float = 1e-6, return_sum: bool = False):
+    """int8 codes and scales of RMSNorm(x + residual); equals
+    quantize_rowwise(residual_rmsnorm(x, residual, weight, eps)) bit for bit."""
+    dev = _need_cuda(x, residual, weight)
+    if residual.shape != x.shape or residual.dtype != x.dtype:
+        raise ValueError("residual must have the shape and dtype of x")
+    if weight.numel() != x.shape[-1]:
+        raise ValueError(f"weight has {weight.numel()} elements, rows have {x.shape[-1]}")
+    x2, r2 = _rows(x), _rows(residual)
+    w = weight.detach().contiguous()
+    codes = torch.empty((x2.shape[0], x2.shape[1]), dtype=torch.int8, device=dev)
+    scales = torch.empty(x2.shape[0], dtype=torch.float32, device=dev)
+    s = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=dev) if return_sum else None
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_residual_rmsnorm_quant_i8(
+            _ptr(x2), _ptr(r2), _ptr(w), _ptr(codes), _ptr(scales), _ptr(s), x2.shape[0],
+            x2.shape[1], _row_stride(x2), _row_stride(r2), x2.shape[1], x2.shape[1], float(eps),
+            _code(x2), _code(w), _stream(dev))
+    _lib.check("trx_residual_rmsnorm_quant_i8", rc)
+    _count()
+    out = (codes.view(x.shape), scales.view(x.shape[:-1]))
+    return out + (s.view(x.shape),) if return_sum else out
+
+
 # ----------------------------------------------------------------------------- RoPE
 def _bshd(t: torch.Tensor) -> torch.Tensor:
     if t.dim() != 4:
