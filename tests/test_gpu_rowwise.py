@@ -124,6 +124,39 @@ def test_quantize_edge_cases_bit_exact(cuda, rows, cols, dtype):
                            ref.view(torch.int16 if out_dtype == torch.bfloat16 else torch.int32))
 
 
+@pytest.mark.parametrize("absmax", [127.0, 254.0, 1.0, 3.1415927, 100.0, 0.0078125, 12345.678])
+def test_quantize_rounding_boundaries_bit_exact(cuda, absmax):
+    """Quotients on and within a few fp32 ulps of every half-integer: the kernel's two-FMA
+    bracket must hand exactly these values to its exact-quotient path, so codes stay bit-exact
+    (the oracle rounds the IEEE quotient half to even)."""
+    scale = np.float32(absmax) / np.float32(127.0)
+    halves = (np.arange(-127, 127, dtype=np.float32) + np.float32(0.5))     # k + 0.5
+    centre = (halves * scale).astype(np.float32)                           # x with x/scale ~ k+0.5
+    rows = []
+    for step in range(-6, 7):                                              # +- 6 ulps around it
+        v = centre.copy()
+        for _ in range(abs(step)):
+            v = np.nextafter(v, np.float32(np.inf if step > 0 else -np.inf)).astype(np.float32)
+        rows.append(v)
+    x = torch.from_numpy(np.stack(rows))
+    x = torch.cat([x, torch.full((x.shape[0], 2), float(absmax))], dim=1)  # fixes the row absmax
+    x = torch.nn.functional.pad(x, (0, (-x.shape[1]) % 8)).contiguous()
+    assert float(x.abs().max()) == float(np.float32(absmax))
+    codes, scales = T.quantize_rowwise(x.to(cuda))
+    _assert_quant_exact(x, codes, scales)
+    # same, with the fp32 row long enough for the multi-warp configurations
+    xl = x.repeat(1, 20).contiguous()
+    codes, scales = T.quantize_rowwise(xl.to(cuda))
+    _assert_quant_exact(xl, codes, scales)
+    # 16-bit inputs: nearest representable values to the boundaries
+    for dtype in (torch.bfloat16, torch.float16):
+        xd = xl.to(dtype)
+        if not torch.isfinite(xd.float()).all():
+            continue
+        codes, scales = T.quantize_rowwise(xd.to(cuda))
+        _assert_quant_exact(xd, codes, scales)
+
+
 def test_quantize_extreme_scales_bit_exact(cuda):
     g = torch.Generator().manual_seed(9)
     x = torch.randn(6, 512, generator=g)

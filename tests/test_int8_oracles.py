@@ -112,3 +112,44 @@ def test_magic_number_rounding_is_half_even():
     y = q + np.float32(12582912.0)
     low = (y.view(np.uint32) & 0xFF).astype(np.uint8).view(np.int8)
     assert np.array_equal(low, np.rint(q).astype(np.int8))
+
+
+def test_two_fma_bracket_never_disagrees_with_ieee_quotient():
+    """The CUDA encoder's fast path: t_lo = rint(x*rcp_lo), t_hi = rint(x*rcp_hi) (each a single
+    rounding of an exact product) with rcp_lo/hi = r * (1 -/+ 2^-21), r = the hardware's
+    approximate 1/scale (within 2^-23; modelled here at both ends of a 2^-22 band and exact).
+    Whenever the two agree they must equal rint(RN(x/scale)); the values where they differ
+    (handed to the exact path) must be rare. Products of two fp32 values are exact in float64."""
+    rng = np.random.default_rng(0)
+    f32 = np.float32
+    total = differ = 0
+    for absmax in [1.0, 127.0, 3.1415927, 4.7, 100.0, 1e-3, 7.7e4, 0.33333334] + list(
+            np.exp(rng.uniform(-20, 20, size=24))):
+        scale = f32(absmax) / f32(127.0)
+        # random values, plus a cloud of values a few ulps around every rounding boundary
+        x = rng.uniform(-1.0, 1.0, size=200_000).astype(f32) * f32(absmax)
+        halves = (np.arange(-127, 127, dtype=f32) + f32(0.5)) * scale
+        cloud = [halves]
+        for _ in range(8):
+            cloud.append(np.nextafter(cloud[-1], f32(np.inf)).astype(f32))
+        cloud.append(halves)
+        for _ in range(8):
+            cloud.append(np.nextafter(cloud[-1], f32(-np.inf)).astype(f32))
+        x = np.concatenate([x] + cloud)
+        x = x[np.abs(x) <= f32(absmax)]
+        xb = N.bf16_bits_to_f32(N.f32_to_bf16_bits(x))  # what the benchmark feeds
+        xb = xb[np.abs(xb) <= f32(absmax)]
+        for rel in (-2.0 ** -22, 0.0, 2.0 ** -22):
+            r = f32(np.float64(1.0) / np.float64(scale) * (1.0 + rel))
+            rcp_lo = f32(r * f32(1.0 - 2.0 ** -21))
+            rcp_hi = f32(r * f32(1.0 + 2.0 ** -21))
+            for v in (x, xb):
+                want = np.rint(v / scale)  # IEEE fp32 division, then half-even
+                lo = np.rint(v.astype(np.float64) * np.float64(rcp_lo))
+                hi = np.rint(v.astype(np.float64) * np.float64(rcp_hi))
+                same = lo == hi
+                assert np.array_equal(lo[same], want[same].astype(np.float64))
+                if v is x:
+                    total += 200_000
+                    differ += int((~same[:200_000]).sum())
+    assert differ / total < 1e-3, differ / total

@@ -74,13 +74,19 @@ struct Pack<__nv_bfloat16> {
   }
   using AbsAcc = __nv_bfloat162;
   __device__ __forceinline__ static AbsAcc absacc_init() { return __float2bfloat162_rn(0.0f); }
+  // max(|a|, |b|) per lane in one instruction (the sign of the result is a don't-care xor)
+  __device__ __forceinline__ static uint32_t absmax2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
   __device__ __forceinline__ static void absacc(const uint4& r, AbsAcc& a) {
-    const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&r);
-    a = __hmax2(a, __hmax2(__hmax2(__habs2(v[0]), __habs2(v[1])),
-                           __hmax2(__habs2(v[2]), __habs2(v[3]))));
+    const uint32_t m = absmax2(absmax2(r.x, r.y), absmax2(r.z, r.w));
+    const uint32_t n = absmax2(*reinterpret_cast<const uint32_t*>(&a), m);
+    a = *reinterpret_cast<const __nv_bfloat162*>(&n);
   }
   __device__ __forceinline__ static float absacc_final(const AbsAcc& a) {
-    return fmaxf(__bfloat162float(a.x), __bfloat162float(a.y));
+    return fmaxf(fabsf(__bfloat162float(a.x)), fabsf(__bfloat162float(a.y)));
   }
   __device__ __forceinline__ static uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -124,13 +130,18 @@ struct Pack<__half> {
   }
   using AbsAcc = __half2;
   __device__ __forceinline__ static AbsAcc absacc_init() { return __float2half2_rn(0.0f); }
+  __device__ __forceinline__ static uint32_t absmax2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.xorsign.abs.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+  }
   __device__ __forceinline__ static void absacc(const uint4& r, AbsAcc& a) {
-    const __half2* v = reinterpret_cast<const __half2*>(&r);
-    a = __hmax2(a, __hmax2(__hmax2(__habs2(v[0]), __habs2(v[1])),
-                           __hmax2(__habs2(v[2]), __habs2(v[3]))));
+    const uint32_t m = absmax2(absmax2(r.x, r.y), absmax2(r.z, r.w));
+    const uint32_t n = absmax2(*reinterpret_cast<const uint32_t*>(&a), m);
+    a = *reinterpret_cast<const __half2*>(&n);
   }
   __device__ __forceinline__ static float absacc_final(const AbsAcc& a) {
-    return fmaxf(__low2float(a), __high2float(a));
+    return fmaxf(fabsf(__low2float(a)), fabsf(__high2float(a)));
   }
   __device__ __forceinline__ static uint32_t pack2(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
@@ -155,6 +166,11 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
                : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
                : "l"(p));
   return r;
+}
+// Ask the copy engine to bring `bytes` (a multiple of 16, from a 16-byte aligned address) into
+// L2. One instruction, no completion to wait for.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void st_stream16(void* p, const uint4& v) {
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
@@ -314,19 +330,41 @@ __device__ __forceinline__ float2 add2(const float2& a, const float2& b) {
 // Per-row constants of the int8 encoder.
 struct QuantRow {
   float scale;   // absmax / 127 (IEEE division)
-  float nscale;  // -scale
-  float rcp;     // RN(1 / scale)
-  int mode;      // 0: zero row, 1: FMA-refined quotient, 2: plain IEEE division
+  float rcp_lo;  // below 1/scale by 2^-24 .. 2^-20 relative
+  float rcp_hi;  // above 1/scale by 2^-24 .. 2^-20 relative
+  int mode;      // 0: zero row, 1: bracketed / FMA-refined quotient, 2: plain IEEE division
 };
 __device__ __forceinline__ QuantRow make_quant_row(float absmax) {
   QuantRow q;
   q.scale = __fdiv_rn(absmax, 127.0f);
-  q.nscale = -q.scale;
-  q.rcp = __frcp_rn(q.scale);
+  // hardware reciprocal: within 2^-23 relative of 1/scale (the bound used below is 2^-22)
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(q.scale));
+  q.rcp_lo = __fmul_rn(r, 1.0f - 0x1p-21f);
+  q.rcp_hi = __fmul_rn(r, 1.0f + 0x1p-21f);
   // The refined quotient below equals the IEEE quotient whenever no intermediate
   // can underflow or overflow; keep it to scales comfortably inside the normal range.
   q.mode = !(q.scale > 0.0f) ? 0 : ((q.scale > 1e-18f && q.scale < 1e18f) ? 1 : 2);
   return q;
+}
+
+// Fast int8 encoder for mode-1 rows: two codes from two FMAs each, no quotient at all.
+// t_lo = RN(x*rcp_lo + 1.5*2^23) and t_hi = RN(x*rcp_hi + 1.5*2^23) are each a single rounding
+// of an exact product to the integer grid (half to even). With rho = 1/scale, r within 2^-22 of
+// rho and one more rounding (2^-24) in each bracket, rcp_lo <= rho*(1 - 3*2^-24) and rcp_hi >=
+// rho*(1 + 3*2^-24), while the IEEE quotient Q = RN(x/scale) is within 2^-24 of x*rho: Q lies
+// strictly between x*rcp_lo and x*rcp_hi. Rounding to the integer grid is monotonic, so
+// t_lo == t_hi implies RN(Q + 1.5*2^23) is that same value, i.e. the low byte of t_lo is
+// rint(Q). When the two differ (Q within ~|Q|*2^-20 of a half-integer, a few values in 10^5)
+// `differ` becomes non-zero and the caller re-encodes with quant_pair<1>.
+__device__ __forceinline__ void quant_pair_bracketed(const float2& x, const QuantRow& qr,
+                                                     uint32_t& b0, uint32_t& b1, uint32_t& differ) {
+  const float2 magic = make_float2(12582912.0f, 12582912.0f);
+  const float2 lo = fma2(x, make_float2(qr.rcp_lo, qr.rcp_lo), magic);
+  const float2 hi = fma2(x, make_float2(qr.rcp_hi, qr.rcp_hi), magic);
+  b0 = __float_as_uint(lo.x);
+  b1 = __float_as_uint(lo.y);
+  differ |= (b0 ^ __float_as_uint(hi.x)) | (b1 ^ __float_as_uint(hi.y));
 }
 
 // Two int8 codes at once. The quotient x/scale is formed as q = x*rcp followed by FMA
@@ -345,8 +383,9 @@ __device__ __forceinline__ void quant_pair(const float2& x, const QuantRow& qr, 
                                            uint32_t& b1) {
   float2 q;
   if constexpr (MODE == 1) {
-    const float2 r = make_float2(qr.rcp, qr.rcp);
-    const float2 ns = make_float2(qr.nscale, qr.nscale);
+    const float rcp = __frcp_rn(qr.scale);  // this path is rare: not worth a register per row
+    const float2 r = make_float2(rcp, rcp);
+    const float2 ns = make_float2(-qr.scale, -qr.scale);
     q = mul2(x, r);
     float2 e = fma2(q, ns, x);
     q = fma2(e, r, q);

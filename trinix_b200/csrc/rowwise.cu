@@ -30,8 +30,16 @@ namespace trx {
 #endif
 
 // Minimum resident CTAs per SM asked of the compiler (caps registers per thread).
+// How many rows ahead of the one it is loading a CTA asks the copy engine to pull into L2
+// (one bulk-prefetch instruction per row, fire and forget). 0 = off.
+#ifndef TRX_ROW_L2_PREFETCH
+#define TRX_ROW_L2_PREFETCH 1
+#endif
 #ifndef TRX_ROW_MINBLOCKS
-#define TRX_ROW_MINBLOCKS(TPR) ((TPR) > 32 ? ((TPR) <= 256 ? 1024 / (TPR) : 1) : 3)
+#ifndef TRX_ROW_THREADS_PER_SM
+#define TRX_ROW_THREADS_PER_SM 1024
+#endif
+#define TRX_ROW_MINBLOCKS(TPR) ((TPR) > 32 ? ((TPR) <= 256 ? TRX_ROW_THREADS_PER_SM / (TPR) : 1) : 3)
 #endif
 
 enum RowOp {
@@ -107,7 +115,20 @@ __device__ __forceinline__ uint32_t mul_packed16<float>(uint32_t a, uint32_t) {
   return a;  // never used: fp32 rows take the scalar-lane path
 }
 
-template <int OP, typename T, int TPR, int VPT>
+// 1/sqrt(mean + eps) from a row sum: a multiply by 1/C (formed once per thread) and the
+// hardware reciprocal square root (2 ulp). The IEEE divide / sqrt / divide sequence costs ~40
+// instructions per thread and row and buys nothing: the fp32 summation order already differs
+// from any host implementation at that level.
+__device__ __forceinline__ float rsqrt_approx(float v) {
+  float r;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// FULL: every row has exactly TPR * VPT vectors and the row count is a multiple of the rows per
+// CTA, so no vector of any thread is padding. The guards disappear, and with them some thirty
+// branches per warp and row that kept the four vectors of a thread from being scheduled together.
+template <int OP, typename T, int TPR, int VPT, bool FULL>
 __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
                                   (op_has_res(OP) && TPR > 32 && TPR <= 256) ? 768 / TPR
                                                                                : TRX_ROW_MINBLOCKS(TPR))
@@ -127,26 +148,44 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
   const int t = threadIdx.x % TPR;
   const int row_in_cta = threadIdx.x / TPR;
   const int nvec = static_cast<int>(p.C / VEC);
+  const float inv_C = __fdiv_rn(1.0f, static_cast<float>(p.C));
 
   const int64_t row_step = static_cast<int64_t>(gridDim.x) * ROWS_PER_CTA;
   // fp32 copies of the row are kept between the statistics and the normalise pass when they
   // fit (saves re-unpacking); longer per-thread slices unpack twice instead.
-  constexpr bool KEEP_F32 = (VEC == 8) && (VPT <= 4) && HAS_NORM;
+#ifndef TRX_ROW_KEEP_F32
+#define TRX_ROW_KEEP_F32 1
+#endif
+  constexpr bool KEEP_F32 = (VEC == 8) && (VPT <= 4) && HAS_NORM && (TRX_ROW_KEEP_F32 || HAS_RES);
 
   for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * ROWS_PER_CTA; row0 < p.R;
        row0 += row_step) {
     const int64_t row = row0 + row_in_cta;
-    const bool row_ok = row < p.R;
+    const bool row_ok = FULL || row < p.R;
+    auto live = [&](int i) -> bool { return FULL || (row_ok && i * TPR + t < nvec); };
 
     // ---- 1. the one and only HBM read of the row ------------------------------------
     uint4 raw[VPT];
     {
-      const T* xrow = reinterpret_cast<const T*>(p.x) + (row_ok ? row : 0) * p.x_stride;
+      const T* xrow = reinterpret_cast<const T*>(p.x) + (FULL || row_ok ? row : 0) * p.x_stride;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int v = i * TPR + t;
-        raw[i] = (row_ok && v < nvec) ? ld_stream16(xrow + static_cast<int64_t>(v) * VEC)
+        raw[i] = live(i) ? ld_stream16(xrow + static_cast<int64_t>(v) * VEC)
                                       : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    // Measured per op: it pays where a row costs two HBM streams (residual forms, +10-16 %) or
+    // two passes over the registers (LayerNorm, +4 %), and costs 5-8 % on the others.
+        if constexpr (TRX_ROW_L2_PREFETCH > 0 && (HAS_RES || OP == OP_LAYERNORM)) {
+      // While this row is in flight, have the row this CTA takes next pulled from HBM into L2, so
+      // that its loads find it there: the only rows a CTA waits for at HBM latency are its first.
+      const int64_t prow = row + TRX_ROW_L2_PREFETCH * row_step;
+      if (t == 0 && prow < p.R) {
+        const uint32_t row_bytes = static_cast<uint32_t>(nvec) * 16u;
+        l2_prefetch_bulk(reinterpret_cast<const T*>(p.x) + prow * p.x_stride, row_bytes);
+        if constexpr (HAS_RES)
+          l2_prefetch_bulk(reinterpret_cast<const T*>(rp.res) + prow * rp.res_stride, row_bytes);
       }
     }
     float2 xf[KEEP_F32 ? VPT : 1][VEC / 2];
@@ -155,19 +194,19 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
     float mean = 0.0f, rstd = 1.0f;
     // ---- 2. statistics -------------------------------------------------------------
     if constexpr (op_is_rms(OP)) {
-      float2 ss2 = make_float2(0.0f, 0.0f);
+      float2 ss2 = make_float2(0.0f, 0.0f), ss2b = make_float2(0.0f, 0.0f);  // two chains
       // residual variants: the host guarantees a configuration that keeps fp32 copies
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         float2 f2[VEC / 2];
         P::unpack2(raw[i], f2);
         if constexpr (HAS_RES) {
-          const T* rrow = reinterpret_cast<const T*>(rp.res) + (row_ok ? row : 0) * rp.res_stride;
-          T* srow = reinterpret_cast<T*>(rp.sum_out) + (row_ok ? row : 0) * rp.sum_stride;
+          const T* rrow = reinterpret_cast<const T*>(rp.res) + (FULL || row_ok ? row : 0) * rp.res_stride;
+          T* srow = reinterpret_cast<T*>(rp.sum_out) + (FULL || row_ok ? row : 0) * rp.sum_stride;
           // residual stream: the sum is formed and normalised in fp32, as the reference's
           // PyTorch path does (layers/fused/residual_rmsnorm.py:66-73)
           const int v = i * TPR + t;
-          if (row_ok && v < nvec) {
+          if (live(i)) {
             const int64_t col = static_cast<int64_t>(v) * VEC;
             float2 r2[VEC / 2];
             P::unpack2(ld_stream16(rrow + col), r2);
@@ -186,13 +225,14 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
         }
 #pragma unroll
         for (int j = 0; j < VEC / 2; ++j) {
-          ss2 = fma2(f2[j], f2[j], ss2);
+          if (j & 1) ss2b = fma2(f2[j], f2[j], ss2b);
+          else ss2 = fma2(f2[j], f2[j], ss2);
           if constexpr (KEEP_F32) xf[i][j] = f2[j];
         }
       }
+      ss2 = add2(ss2, ss2b);
       float ss = row_reduce<TPR, false>(ss2.x + ss2.y, red, sel);
-      const float var = __fdiv_rn(ss, static_cast<float>(p.C));
-      rstd = __fdiv_rn(1.0f, __fsqrt_rn(var + p.eps));
+      rstd = rsqrt_approx(fmaf(ss, inv_C, p.eps));
     } else if constexpr (OP == OP_LAYERNORM) {
       float2 s2 = make_float2(0.0f, 0.0f);
 #pragma unroll
@@ -206,13 +246,13 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
         }
       }
       const float s = row_reduce<TPR, false>(s2.x + s2.y, red, sel);
-      mean = __fdiv_rn(s, static_cast<float>(p.C));
+      mean = s * inv_C;
       const float2 nmean2 = make_float2(-mean, -mean);
       float2 cs2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int v = i * TPR + t;
-        if (v < nvec) {  // padding vectors must not contribute (0 - mean)^2
+        if (FULL || v < nvec) {  // padding vectors must not contribute (0 - mean)^2
           float2 f2[VEC / 2];
           if constexpr (KEEP_F32) {
 #pragma unroll
@@ -229,8 +269,7 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
       }
       float cs = cs2.x + cs2.y;
       cs = row_reduce<TPR, false>(cs, red, sel);
-      const float var = __fdiv_rn(cs, static_cast<float>(p.C));
-      rstd = __fdiv_rn(1.0f, __fsqrt_rn(var + p.eps));
+      rstd = rsqrt_approx(fmaf(cs, inv_C, p.eps));
     }
     if constexpr (HAS_NORM) {
       if (row_ok && t == 0) {
@@ -244,7 +283,7 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
     if constexpr (HAS_NORM) {
       T* yrow = NORM_TO_REGS
                     ? nullptr
-                    : reinterpret_cast<T*>(p.y) + (row_ok ? row : 0) * p.y_stride;
+                    : reinterpret_cast<T*>(p.y) + (FULL || row_ok ? row : 0) * p.y_stride;
       auto emit = [&](int i, int64_t col, const uint4& packed) {
         if constexpr (NORM_TO_REGS) {
           raw[i] = packed;
@@ -256,7 +295,7 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int v = i * TPR + t;
-          if (row_ok && v < nvec) {
+          if (live(i)) {
             float f[VEC];
             if constexpr (KEEP_F32) {
 #pragma unroll
@@ -295,7 +334,7 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
               const int v = i * TPR + t;
-              if (row_ok && v < nvec) {
+              if (live(i)) {
                 const int64_t col = static_cast<int64_t>(v) * VEC;
                 const uint4 wraw = ld_cached16(reinterpret_cast<const T*>(p.w) + col);
                 const uint32_t* wu = reinterpret_cast<const uint32_t*>(&wraw);
@@ -321,7 +360,7 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
 #pragma unroll
           for (int i = 0; i < VPT; ++i) {
             const int v = i * TPR + t;
-            if (row_ok && v < nvec) {
+            if (live(i)) {
               float f[VEC];
               P::unpack(raw[i], f);
               const int64_t col = static_cast<int64_t>(v) * VEC;
@@ -345,19 +384,31 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
       const float am = row_reduce<TPR, true>(P::absacc_final(acc), red, sel);
       const QuantRow qr = make_quant_row(am);
       if (row_ok && t == 0) p.scales[row] = qr.scale;
-      int8_t* crow = p.codes + (row_ok ? row : 0) * p.codes_stride;
+      int8_t* crow = p.codes + (FULL || row_ok ? row : 0) * p.codes_stride;
       auto encode_row = [&](auto mode_tag) {
         constexpr int MODE = decltype(mode_tag)::value;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int v = i * TPR + t;
-          if (row_ok && v < nvec) {
-            float2 f2[VEC / 2];
-            P::unpack2(raw[i], f2);
+          float2 f2[VEC / 2];
+          P::unpack2(raw[i], f2);
+          if (live(i)) {
             uint32_t yb[VEC];
+            bool exact_path = (MODE != 1);
+            if constexpr (MODE == 1) {
+              uint32_t differ = 0u;
 #pragma unroll
-            for (int j = 0; j < VEC / 2; ++j)
-              quant_pair<MODE, (VEC == 8)>(f2[j], qr, yb[2 * j], yb[2 * j + 1]);
+              for (int j = 0; j < VEC / 2; ++j)
+                quant_pair_bracketed(f2[j], qr, yb[2 * j], yb[2 * j + 1], differ);
+              // a quotient too close to a rounding boundary: about one vector in 10^4. Voted so
+              // that the branch is uniform and stays a branch.
+              exact_path = __any_sync(__activemask(), differ != 0u);
+            }
+            if (exact_path) {
+#pragma unroll
+              for (int j = 0; j < VEC / 2; ++j)
+                quant_pair<MODE, (VEC == 8)>(f2[j], qr, yb[2 * j], yb[2 * j + 1]);
+            }
             int8_t* dst = crow + static_cast<int64_t>(v) * VEC;
             if constexpr (VEC == 8) {
               st_stream8(dst, make_uint2(pack_low_bytes(yb[0], yb[1], yb[2], yb[3]),
@@ -384,6 +435,7 @@ __global__ void __launch_bounds__(256) row_kernel_generic(const RowParamsBase p,
   __shared__ __align__(16) float red[2][32];
   int sel = 0;
   constexpr bool HAS_QUANT = op_has_quant(OP);
+  const float inv_C = __fdiv_rn(1.0f, static_cast<float>(p.C));
   for (int64_t row = blockIdx.x; row < p.R; row += gridDim.x) {
     const T* xrow = reinterpret_cast<const T*>(p.x) + row * p.x_stride;
     float mean = 0.0f, rstd = 1.0f;
@@ -405,19 +457,19 @@ __global__ void __launch_bounds__(256) row_kernel_generic(const RowParamsBase p,
         if (srow) P::store1(srow + c, f);
       }
       ss = row_reduce<256, false>(ss, red, sel);
-      rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(ss, static_cast<float>(p.C)) + p.eps));
+      rstd = rsqrt_approx(fmaf(ss, inv_C, p.eps));
     } else if constexpr (OP == OP_LAYERNORM) {
       float s = 0.0f;
       for (int64_t c = threadIdx.x; c < p.C; c += 256) s += P::load1(xrow + c);
       s = row_reduce<256, false>(s, red, sel);
-      mean = __fdiv_rn(s, static_cast<float>(p.C));
+      mean = s * inv_C;
       float cs = 0.0f;
       for (int64_t c = threadIdx.x; c < p.C; c += 256) {
         const float d = P::load1(xrow + c) - mean;
         cs = fmaf(d, d, cs);
       }
       cs = row_reduce<256, false>(cs, red, sel);
-      rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fdiv_rn(cs, static_cast<float>(p.C)) + p.eps));
+      rstd = rsqrt_approx(fmaf(cs, inv_C, p.eps));
     }
     if (OP != OP_QUANT && threadIdx.x == 0) {
       if (p.rstd) p.rstd[row] = rstd;
@@ -469,15 +521,20 @@ static int sm_count_of_current_device() {
   return cached[dev];
 }
 
-template <int OP, typename T, int TPR, int VPT>
-static int launch_cfg(const RowParams& p, cudaStream_t stream) {
+template <int OP, typename T, int TPR, int VPT, bool FULL>
+static int launch_cfg_full(const RowParams& p, cudaStream_t stream) {
   constexpr int BLOCK = TPR > 32 ? TPR : 256;
   constexpr int ROWS_PER_CTA = BLOCK / TPR;
-  static int blocks_per_sm = 0;  // same for every sm_100a device
+  // The occupancy answer is cached per device ordinal.
+  static int blocks_per_sm_of[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return TRX_ERR_CUDA;
+  int uncached = 0;
+  int& blocks_per_sm = (dev >= 0 && dev < 64) ? blocks_per_sm_of[dev] : uncached;
   if (blocks_per_sm == 0) {
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, row_kernel<OP, T, TPR, VPT>, BLOCK, 0) !=
-            cudaSuccess ||
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, row_kernel<OP, T, TPR, VPT, FULL>, BLOCK,
+                                                      0) != cudaSuccess ||
         n <= 0)
       n = 1;
     blocks_per_sm = n;
@@ -485,8 +542,18 @@ static int launch_cfg(const RowParams& p, cudaStream_t stream) {
   const int64_t need = (p.R + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
   const int64_t cap = static_cast<int64_t>(sm_count_of_current_device()) * blocks_per_sm;
   const unsigned grid = static_cast<unsigned>(need < cap ? need : cap);
-  row_kernel<OP, T, TPR, VPT><<<grid, BLOCK, 0, stream>>>(static_cast<const RowParamsBase&>(p), res_arg<OP>(p));
+  row_kernel<OP, T, TPR, VPT, FULL><<<grid, BLOCK, 0, stream>>>(static_cast<const RowParamsBase&>(p), res_arg<OP>(p));
   return cudaGetLastError() == cudaSuccess ? TRX_OK : TRX_ERR_CUDA;
+}
+
+template <int OP, typename T, int TPR, int VPT>
+static int launch_cfg(const RowParams& p, cudaStream_t stream) {
+  constexpr int ROWS_PER_CTA = (TPR > 32 ? TPR : 256) / TPR;
+  if constexpr (VPT <= 4) {  // the specialisation is built where rows of that exact width matter
+    if (p.C / Pack<T>::VEC == TPR * VPT && p.R % ROWS_PER_CTA == 0)
+      return launch_cfg_full<OP, T, TPR, VPT, true>(p, stream);
+  }
+  return launch_cfg_full<OP, T, TPR, VPT, false>(p, stream);
 }
 
 template <int OP, typename T>
