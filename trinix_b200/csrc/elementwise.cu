@@ -284,7 +284,10 @@ static int launch_rope(const RopeParams& p, int64_t B, cudaStream_t stream) {
 // ----------------------------------------------------------------------------
 // Dequantise
 // ----------------------------------------------------------------------------
-constexpr int DQ_ROWS_PER_THREAD = 8;
+#ifndef TRX_DQ_ROWS
+#define TRX_DQ_ROWS 8
+#endif
+constexpr int DQ_ROWS_PER_THREAD = TRX_DQ_ROWS;
 constexpr int DQ_THREADS = 128;
 
 // int8 -> fp32 without a convert instruction: place (code ^ 0x80) in the low mantissa byte
@@ -358,10 +361,15 @@ static int launch_dequant(const int8_t* codes, const float* scales, void* y, int
   if (vec_ok) {
     const int nvec16 = static_cast<int>(C / 16);
     const int64_t row_blocks = (R + DQ_ROWS_PER_THREAD - 1) / DQ_ROWS_PER_THREAD;
-    // One resident wave: about 8 CTAs of 128 threads per SM in total, each walking over
-    // row blocks, so that a short launch is not split into a full and a nearly empty wave.
+    // About 8 CTAs of 128 threads per SM in total, each walking over row blocks. (Sizing the grid
+    // to exactly one resident wave with equal walks measured 7 % slower: the surplus CTAs let the
+    // hardware scheduler even out the tail.)
+#ifndef TRX_DQ_GRID_MULT
+#define TRX_DQ_GRID_MULT 1
+#endif
     const int64_t col_blocks = (nvec16 + DQ_THREADS - 1) / DQ_THREADS;
-    int64_t y_blocks = (148 * 8 + col_blocks - 1) / col_blocks;
+    int64_t y_blocks = (static_cast<int64_t>(sm_count_of_current_device()) * 8 * TRX_DQ_GRID_MULT +
+                        col_blocks - 1) / col_blocks;
     if (y_blocks > row_blocks) y_blocks = row_blocks;
     if (y_blocks > 65535) y_blocks = 65535;
     if (y_blocks < 1) y_blocks = 1;

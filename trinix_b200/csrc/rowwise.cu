@@ -151,12 +151,10 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
   const float inv_C = __fdiv_rn(1.0f, static_cast<float>(p.C));
 
   const int64_t row_step = static_cast<int64_t>(gridDim.x) * ROWS_PER_CTA;
-  // fp32 copies of the row are kept between the statistics and the normalise pass when they
-  // fit (saves re-unpacking); longer per-thread slices unpack twice instead.
-#ifndef TRX_ROW_KEEP_F32
-#define TRX_ROW_KEEP_F32 1
-#endif
-  constexpr bool KEEP_F32 = (VEC == 8) && (VPT <= 4) && HAS_NORM && (TRX_ROW_KEEP_F32 || HAS_RES);
+  // The residual forms keep the fp32 sum x + r of a 16-bit row on chip between the statistics
+  // and the normalise pass (it exists nowhere else). The other ops unpack the packed row a
+  // second time instead: 32 fewer live registers measured better than 8 fewer instructions.
+  constexpr bool KEEP_F32 = (VEC == 8) && (VPT <= 4) && HAS_RES;
 
   for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * ROWS_PER_CTA; row0 < p.R;
        row0 += row_step) {
@@ -231,6 +229,13 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
         }
       }
       ss2 = add2(ss2, ss2b);
+      if constexpr (VEC == 8 && !KEEP_F32) {
+        // keep the compiler from carrying the fp32 copies across the reduction after all (it
+        // would, by common-subexpression elimination): the packed row is all that stays live
+#pragma unroll
+        for (int i = 0; i < VPT; ++i)
+          asm volatile("" : "+r"(raw[i].x), "+r"(raw[i].y), "+r"(raw[i].z), "+r"(raw[i].w));
+      }
       float ss = row_reduce<TPR, false>(ss2.x + ss2.y, red, sel);
       rstd = rsqrt_approx(fmaf(ss, inv_C, p.eps));
     } else if constexpr (OP == OP_LAYERNORM) {
@@ -508,19 +513,6 @@ __global__ void __launch_bounds__(256) row_kernel_generic(const RowParamsBase p,
 // ----------------------------------------------------------------------------
 // Host-side dispatch
 // ----------------------------------------------------------------------------
-static int sm_count_of_current_device() {
-  static int cached[64] = {0};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 148;
-    cached[dev] = n;
-  }
-  return cached[dev];
-}
-
 template <int OP, typename T, int TPR, int VPT, bool FULL>
 static int launch_cfg_full(const RowParams& p, cudaStream_t stream) {
   constexpr int BLOCK = TPR > 32 ? TPR : 256;
@@ -541,7 +533,15 @@ static int launch_cfg_full(const RowParams& p, cudaStream_t stream) {
   }
   const int64_t need = (p.R + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
   const int64_t cap = static_cast<int64_t>(sm_count_of_current_device()) * blocks_per_sm;
-  const unsigned grid = static_cast<unsigned>(need < cap ? need : cap);
+  // Grid = several resident waves, each CTA striding over a few rows. Exactly one wave of
+  // persistent CTAs measured 5-12 % slower on every op (the hardware scheduler evens out SMs
+  // that run behind); the two ops without an int8 encoder or a second pass do best with one
+  // CTA per row.
+#ifndef TRX_ROW_GRID_MULT
+#define TRX_ROW_GRID_MULT ((OP == OP_RMSNORM || OP == OP_RES_RMSNORM) ? 64 : 8)
+#endif
+  const int64_t want = cap * TRX_ROW_GRID_MULT;
+  const unsigned grid = static_cast<unsigned>(need < want ? need : want);
   row_kernel<OP, T, TPR, VPT, FULL><<<grid, BLOCK, 0, stream>>>(static_cast<const RowParamsBase&>(p), res_arg<OP>(p));
   return cudaGetLastError() == cudaSuccess ? TRX_OK : TRX_ERR_CUDA;
 }
@@ -549,7 +549,10 @@ static int launch_cfg_full(const RowParams& p, cudaStream_t stream) {
 template <int OP, typename T, int TPR, int VPT>
 static int launch_cfg(const RowParams& p, cudaStream_t stream) {
   constexpr int ROWS_PER_CTA = (TPR > 32 ? TPR : 256) / TPR;
-  if constexpr (VPT <= 4) {  // the specialisation is built where rows of that exact width matter
+#ifndef TRX_ROW_FULL_MAX_VPT
+#define TRX_ROW_FULL_MAX_VPT 4
+#endif
+  if constexpr (VPT <= TRX_ROW_FULL_MAX_VPT) {  // built where rows of that exact width matter
     if (p.C / Pack<T>::VEC == TPR * VPT && p.R % ROWS_PER_CTA == 0)
       return launch_cfg_full<OP, T, TPR, VPT, true>(p, stream);
   }
@@ -580,7 +583,12 @@ static int launch_row(const RowParams& p, cudaStream_t stream) {
     if (nvec <= 64) return launch_cfg<OP, T, 32, 2>(p, stream);
     if (nvec <= 128) return launch_cfg<OP, T, 32, 4>(p, stream);
     if (nvec <= 256) return launch_cfg<OP, T, TRX_ROW256_TPR, TRX_ROW256_VPT>(p, stream);
-    if (nvec <= 512) return launch_cfg<OP, T, TRX_ROW512_TPR, TRX_ROW512_VPT>(p, stream);
+    if (nvec <= 512) {
+      // two input streams per row: 256 threads x 2 vectors measured 93-95 % of the copy rate,
+      // 128 x 4 (best for the single-stream ops) 86 %
+      if constexpr (op_has_res(OP)) return launch_cfg<OP, T, 256, 2>(p, stream);
+      else return launch_cfg<OP, T, TRX_ROW512_TPR, TRX_ROW512_VPT>(p, stream);
+    }
     if (nvec <= 1024) return launch_cfg<OP, T, 256, 4>(p, stream);
     if (nvec <= 2048) return launch_cfg<OP, T, 512, 4>(p, stream);
     if (nvec <= 4096) return launch_cfg<OP, T, 1024, 4>(p, stream);
