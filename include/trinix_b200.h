@@ -193,6 +193,30 @@ int trx_attn_fwd(const void* q, const void* k, const void* v, void* out, float* 
                  size_t workspace_bytes, void* stream);
 
 /*
+ * trx_attn_fwd with a dense additive mask: softmax(scale * Q K^T + mask [+ ALiBi]) V.
+ *   mask: (B, Hq, Sq, Sk) values added to the scaled scores (0 keeps, -inf hides); fp32 or the
+ *   activation dtype (mask_dtype); mask_strides = (batch, head, query) in elements, the key
+ *   stride is 1; a batch or head stride of 0 broadcasts, which is how the reference's 2-D
+ *   (Sq, Sk), 3-D (B, Sq, Sk) and 4-D (B, 1, Sq, Sk) masks are passed without expanding them.
+ *   causal / window / ALiBi combine with it; a row whose keys are all hidden returns 0.
+ * Every KV tile a query tile can see is visited (a dense mask gives no tile to skip), and the
+ * mask is read once per score: 4 bytes per score for fp32, so the call is bound by the mask's
+ * HBM traffic unless the mask is broadcast over batch and heads.
+ * Replaces the attn_mask path of TritonAttentionKernel.apply,
+ * trinix/kernels/attention_kernel.py:479-495 (_prepare_mask) and :9-231 (_fwd_kernel_with_mask);
+ * mask semantics of FastBaseAttention._apply_pytorch_attention,
+ * trinix/layers/attention/base.py:381-392.
+ */
+int trx_attn_fwd_mask(const void* q, const void* k, const void* v, void* out, float* lse_or_null,
+                      const float* slopes_or_null, const void* mask, int mask_dtype,
+                      const int64_t mask_strides[3], int64_t B, int64_t Sq, int64_t Sk, int64_t Hq,
+                      int64_t Hk, int64_t D, const int64_t q_strides[3],
+                      const int64_t k_strides[3], const int64_t v_strides[3],
+                      const int64_t o_strides[3], float scale, int causal, int64_t window_left,
+                      int64_t window_right, int dtype, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
+/*
  * trx_attn_fwd for callers that cannot provide a workspace. No counterpart in the reference.
  *
  * Who needs it: hosts that pass pointers in but cannot create device memory when the call is

@@ -163,3 +163,76 @@ def test_full_size_properties(cuda):
         q.transpose(1, 2), k.transpose(1, 2).repeat_interleave(4, 1),
         v.transpose(1, 2).repeat_interleave(4, 1), is_causal=True).transpose(1, 2)
     assert float((out.float() - ref.float()).abs().max()) <= TOL
+
+
+def _mask_ref(q, k, v, mask4, causal, scale=None):
+    """The reference's PyTorch attention (base.py:347-400) with K/V tiled to all query heads
+    and the mask expanded to (B, H, Sq, Sk), in the input dtype and in fp32."""
+    g = q.shape[2] // k.shape[2]
+    kt, vt = k.repeat_interleave(g, dim=2), v.repeat_interleave(g, dim=2)
+    B, Sq, H, _ = q.shape
+    m = mask4.expand(B, H, Sq, k.shape[1]).float()
+    ref = R.attention_ref(q, kt, vt, scale, causal, m.to(q.dtype)).float()
+    ref32 = R.attention_ref(q.float(), kt.float(), vt.float(), scale, causal, m)
+    return ref, ref32
+
+
+@pytest.mark.parametrize("mask_kind", ["2d_f32", "3d_bool", "4d_b1", "4d_bh_bf16"])
+@pytest.mark.parametrize("Sq,Sk,D", [(300, 300, 128), (257, 640, 64)])
+def test_dense_additive_mask(cuda, mask_kind, Sq, Sk, D):
+    """attn_mask in every shape _prepare_mask accepts (attention_kernel.py:479-495), float and
+    bool, broadcast by stride: parity with the reference's PyTorch path on the expanded mask."""
+    B, Hq, Hk = 2, 4, 2
+    q, k, v = _qkv(B, Sq, Sk, Hq, Hk, D, seed=Sq + Sk)
+    g = torch.Generator().manual_seed(7)
+    if mask_kind == "2d_f32":
+        mask = torch.randn(Sq, Sk, generator=g)
+        mask[:, Sk // 3: Sk // 2] = float("-inf")          # a hidden band
+        mask4 = mask[None, None]
+    elif mask_kind == "3d_bool":
+        hidden = torch.rand(B, Sq, Sk, generator=g) < 0.3
+        hidden[..., 0] = False                              # no fully hidden row
+        mask = hidden
+        mask4 = torch.zeros(B, 1, Sq, Sk).masked_fill_(hidden[:, None], float("-inf"))
+    elif mask_kind == "4d_b1":
+        mask = torch.randn(B, 1, Sq, Sk, generator=g) * 2
+        mask4 = mask
+    else:
+        mask = (torch.randn(B, Hq, Sq, Sk, generator=g) * 2).bfloat16()
+        mask4 = mask.float()
+    out = T.triton_attn_func(q.to(cuda), k.to(cuda), v.to(cuda), attn_mask=mask.to(cuda))
+    assert T.attention_status(cuda) == 0
+    ref, ref32 = _mask_ref(q, k, v, mask4, False)
+    o = out.float().cpu()
+    assert not torch.isnan(o).any()
+    err, err32 = float((o - ref).abs().max()), float((o - ref32).abs().max())
+    noise = float((ref - ref32).abs().max())
+    assert err32 <= TOL and err <= TOL + noise, (err, err32, noise)
+
+
+def test_dense_mask_combines_with_causal_and_alibi(cuda):
+    B, S, Hq, Hk, D = 1, 400, 4, 1, 128
+    q, k, v = _qkv(B, S, S, Hq, Hk, D, seed=11)
+    g = torch.Generator().manual_seed(3)
+    mask = torch.randn(S, S, generator=g)
+    slopes = torch.tensor([0.5, 0.25, 0.125, 0.0625])
+    out = T.triton_attn_func(q.to(cuda), k.to(cuda), v.to(cuda), attn_mask=mask.to(cuda),
+                             causal=True, alibi_slopes=slopes.to(cuda))
+    assert T.attention_status(cuda) == 0
+    i = torch.arange(S)
+    alibi = -slopes[:, None, None] * (i[:, None] - i[None, :]).abs().float()   # (H, S, S)
+    ref, ref32 = _mask_ref(q, k, v, (mask[None] + alibi)[None], True)
+    o = out.float().cpu()
+    err, err32 = float((o - ref).abs().max()), float((o - ref32).abs().max())
+    noise = float((ref - ref32).abs().max())
+    assert err32 <= TOL and err <= TOL + noise, (err, err32, noise)
+
+
+def test_dense_mask_rejects_bad_shapes(cuda):
+    q, k, v = (t.to(cuda) for t in _qkv(2, 128, 128, 2, 2, 64))
+    with pytest.raises(ValueError):
+        T.triton_attn_func(q, k, v, attn_mask=torch.zeros(128, 64, device=cuda))
+    with pytest.raises(ValueError):
+        T.triton_attn_func(q, k, v, attn_mask=torch.zeros(3, 128, 128, device=cuda))
+    with pytest.raises(ValueError):
+        T.triton_attn_func(q, k, v, attn_mask=torch.zeros(1, 1, 1, 128, 128, device=cuda))

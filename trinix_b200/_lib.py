@@ -48,6 +48,10 @@ SIGNATURES = {
                              c_int64, c_int64, c_int64, c_int64, c_int64, I64x3, I64x3, I64x3,
                              I64x3, c_float, c_int, c_int64, c_int64, c_int, c_void_p, c_size_t,
                              c_void_p]),
+    "trx_attn_fwd_mask": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_int, I64x3, c_int64, c_int64, c_int64, c_int64,
+                                  c_int64, c_int64, I64x3, I64x3, I64x3, I64x3, c_float, c_int,
+                                  c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
     "trx_attn_fwd_static_scratch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                             c_int64, I64x3, I64x3, I64x3, I64x3, c_float, c_int,

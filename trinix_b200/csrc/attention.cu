@@ -65,6 +65,10 @@ struct AttnParams {
   int win_left, win_right;  // < 0: no window
   int is_bf16;
   int reverse_m;       // schedule the heaviest (last) row blocks first
+  // dense additive mask (B, Hq, Sq, Sk) with unit key stride; batch / head strides may be 0
+  const void* bias;
+  long long bias_sb, bias_sh, bias_sq;  // elements
+  int bias_kind;       // 0 none, 1 fp32, 2 the activation dtype
 };
 
 // ------------------------------------------------------------------------------------------
@@ -597,6 +601,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     const float sl2 = p.scale_log2;
     const float slope2 = p.slopes ? p.slopes[h] * 1.4426950408889634f : 0.0f;
     const bool has_alibi = p.slopes != nullptr;
+    const bool has_bias = p.bias_kind != 0;
+    // rows of the dense mask that this thread's two score rows read (valid rows only)
+    const uint8_t* brow[2] = {nullptr, nullptr};
+    if (has_bias) {
+      const int esz = p.bias_kind == 1 ? 4 : 2;
+#pragma unroll
+      for (int hr = 0; hr < 2; ++hr)
+        if (row0 + rl + 8 * hr < p.Sq)
+          brow[hr] = reinterpret_cast<const uint8_t*>(p.bias) +
+                     esz * (b * p.bias_sb + h * p.bias_sh +
+                            static_cast<long long>(row0 + rl + 8 * hr) * p.bias_sq);
+    }
 
     float m_run[2] = {-INFINITY, -INFINITY};  // reference max (log2 domain) per row
     float l_run[2] = {0.0f, 0.0f};            // this thread's share of the row sums
@@ -623,7 +639,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         else if (c0 >= row1) alibi_sgn = -1;          // every key at or after every query
       }
       // general path: a tile that straddles the diagonal under ALiBi, or a non-positive scale
-      const bool general = (has_alibi && alibi_sgn == 0) || !(sl2 > 0.0f);
+      const bool general = (has_alibi && alibi_sgn == 0) || !(sl2 > 0.0f) || has_bias;
       float m_tile[2] = {-INFINITY, -INFINITY};
       float off[2] = {0.0f, 0.0f};  // fast path: x = t * sl2 + off
       if (general) {
@@ -637,6 +653,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
               const int i = 4 * g + 2 * hr + e;
               float x = __uint_as_float(sr[i]) * sl2;
               if (has_alibi) x = fmaf(-slope2, fabsf(fi - static_cast<float>(8 * g + e)), x);
+              if (has_bias) {
+                const int col = c0 + 8 * g + 2 * q4 + e;
+                if (brow[hr] != nullptr && col < p.Sk) {
+                  float bv;
+                  if (p.bias_kind == 1) bv = reinterpret_cast<const float*>(brow[hr])[col];
+                  else if (BF16) bv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(brow[hr])[col]);
+                  else bv = __half2float(reinterpret_cast<const __half*>(brow[hr])[col]);
+                  x = fmaf(bv, 1.4426950408889634f, x);  // -inf stays -inf
+                }
+              }
               if (need_mask) {
                 const int col = c0 + 8 * g + 2 * q4 + e;
                 if (col < lo_i[hr] || col > hi_i[hr]) x = -INFINITY;
@@ -948,14 +974,22 @@ using namespace trx;
 
 extern "C" size_t trx_attn_workspace_bytes(void) { return 256; }
 
-extern "C" int trx_attn_fwd(const void* q, const void* k, const void* v, void* out,
-                            float* lse_or_null, const float* slopes_or_null, int64_t B, int64_t Sq,
-                            int64_t Sk, int64_t Hq, int64_t Hk, int64_t D,
-                            const int64_t q_strides[3], const int64_t k_strides[3],
-                            const int64_t v_strides[3], const int64_t o_strides[3], float scale,
-                            int causal, int64_t window_left, int64_t window_right, int dtype,
-                            void* workspace, size_t workspace_bytes, void* stream) {
+// Shared body of the attention entry points. `bias` may be null (no dense mask).
+static int attn_fwd_impl(const void* q, const void* k, const void* v, void* out,
+                         float* lse_or_null, const float* slopes_or_null, const void* bias,
+                         int bias_dtype, const int64_t* bias_strides, int64_t B, int64_t Sq,
+                         int64_t Sk, int64_t Hq, int64_t Hk, int64_t D,
+                         const int64_t q_strides[3], const int64_t k_strides[3],
+                         const int64_t v_strides[3], const int64_t o_strides[3], float scale,
+                         int causal, int64_t window_left, int64_t window_right, int dtype,
+                         void* workspace, size_t workspace_bytes, void* stream) {
   if (dtype != TRX_BF16 && dtype != TRX_F16) return TRX_ERR_DTYPE;
+  if (bias) {
+    if (bias_dtype != TRX_F32 && bias_dtype != dtype) return TRX_ERR_DTYPE;
+    if (!bias_strides) return TRX_ERR_NULL_POINTER;
+    if (bias_strides[0] < 0 || bias_strides[1] < 0 || bias_strides[2] < Sk)
+      return TRX_ERR_STRIDE;
+  }
   if (B < 0 || Sq < 0 || Sk < 0 || Hq <= 0 || Hk <= 0 || D <= 0) return TRX_ERR_SHAPE;
   if (Hq % Hk != 0) return TRX_ERR_SHAPE;
   if (D != 64 && D != 128) return TRX_ERR_UNSUPPORTED;
@@ -1015,9 +1049,43 @@ extern "C" int trx_attn_fwd(const void* q, const void* k, const void* v, void* o
   p.win_right = window_right < 0 ? -1 : static_cast<int>(window_right > (1ll << 29) ? (1ll << 29) : window_right);
   p.is_bf16 = is_bf16;
   p.reverse_m = causal ? 1 : 0;
+  if (bias && Sk > 0) {
+    p.bias = bias;
+    p.bias_sb = bias_strides[0];
+    p.bias_sh = bias_strides[1];
+    p.bias_sq = bias_strides[2];
+    p.bias_kind = bias_dtype == TRX_F32 ? 1 : 2;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 128) return is_bf16 ? launch_attn<128, true>(p, s) : launch_attn<128, false>(p, s);
   return is_bf16 ? launch_attn<64, true>(p, s) : launch_attn<64, false>(p, s);
+}
+
+extern "C" int trx_attn_fwd(const void* q, const void* k, const void* v, void* out,
+                            float* lse_or_null, const float* slopes_or_null, int64_t B, int64_t Sq,
+                            int64_t Sk, int64_t Hq, int64_t Hk, int64_t D,
+                            const int64_t q_strides[3], const int64_t k_strides[3],
+                            const int64_t v_strides[3], const int64_t o_strides[3], float scale,
+                            int causal, int64_t window_left, int64_t window_right, int dtype,
+                            void* workspace, size_t workspace_bytes, void* stream) {
+  return attn_fwd_impl(q, k, v, out, lse_or_null, slopes_or_null, nullptr, 0, nullptr, B, Sq, Sk,
+                       Hq, Hk, D, q_strides, k_strides, v_strides, o_strides, scale, causal,
+                       window_left, window_right, dtype, workspace, workspace_bytes, stream);
+}
+
+extern "C" int trx_attn_fwd_mask(const void* q, const void* k, const void* v, void* out,
+                                 float* lse_or_null, const float* slopes_or_null,
+                                 const void* mask, int mask_dtype, const int64_t mask_strides[3],
+                                 int64_t B, int64_t Sq, int64_t Sk, int64_t Hq, int64_t Hk,
+                                 int64_t D, const int64_t q_strides[3],
+                                 const int64_t k_strides[3], const int64_t v_strides[3],
+                                 const int64_t o_strides[3], float scale, int causal,
+                                 int64_t window_left, int64_t window_right, int dtype,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+  if (!mask) return TRX_ERR_NULL_POINTER;
+  return attn_fwd_impl(q, k, v, out, lse_or_null, slopes_or_null, mask, mask_dtype, mask_strides,
+                       B, Sq, Sk, Hq, Hk, D, q_strides, k_strides, v_strides, o_strides, scale,
+                       causal, window_left, window_right, dtype, workspace, workspace_bytes, stream);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -137,8 +137,10 @@ class TritonAttentionKernel:
     """Same interface as trinix/kernels/attention_kernel.py:436-664.
 
     Differences, all widening: k/v may have fewer heads than q (grouped / multi-query
-    attention without tiling copies) and a different sequence length. `attn_mask` and
-    `dropout_p > 0` are not implemented and raise instead of silently taking another path.
+    attention without tiling copies) and a different sequence length. `attn_mask` follows
+    `_prepare_mask` (attention_kernel.py:479-495): 2-D (Sq, Sk), 3-D (B, Sq, Sk) or 4-D
+    (B, 1 | H, Sq, Sk), additive, read through its broadcast strides. `dropout_p > 0` is not
+    implemented and raises instead of silently taking another path.
     """
 
     @staticmethod
@@ -151,13 +153,12 @@ class TritonAttentionKernel:
               scale: Optional[float] = None, dropout_p: float = 0.0,
               window_size: Optional[tuple] = None,
               alibi_slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if attn_mask is not None:
-            raise NotImplementedError("trinix_b200 attention: dense attn_mask is not implemented")
         if dropout_p and dropout_p > 0.0:
             raise NotImplementedError("trinix_b200 attention: dropout is not implemented")
         return _run(
             lambda a, b, c: ops.attention(a, b, c, causal=causal, scale=scale,
-                                          window=window_size, alibi_slopes=alibi_slopes),
+                                          window=window_size, alibi_slopes=alibi_slopes,
+                                          attn_mask=attn_mask),
             q, k, v)
 
 

@@ -327,15 +327,49 @@ def attention_status(device=None) -> int:
     return word
 
 
+def _dense_mask(mask: torch.Tensor, B: int, Hq: int, Sq: int, Sk: int, act_dtype):
+    """The mask as the kernel reads it: fp32 or the activation dtype, unit key stride, and the
+    (batch, head, query) element strides of its broadcast view (shape rules of
+    TritonAttentionKernel._prepare_mask, trinix/kernels/attention_kernel.py:479-495)."""
+    m = mask.detach()
+    if m.dtype == torch.bool:
+        m = torch.zeros(m.shape, dtype=torch.float32, device=m.device).masked_fill_(m, float("-inf"))
+    elif m.dtype not in (torch.float32, act_dtype):
+        m = m.to(torch.float32)
+    if m.dim() == 2:
+        m = m[None, None]
+    elif m.dim() == 3:
+        m = m[:, None]
+    elif m.dim() != 4:
+        raise ValueError(f"Unsupported mask shape: {tuple(mask.shape)}")
+    if m.shape[-2:] != (Sq, Sk) or m.shape[0] not in (1, B) or m.shape[1] not in (1, Hq):
+        raise ValueError(f"mask shape {tuple(mask.shape)} does not broadcast to "
+                         f"({B}, {Hq}, {Sq}, {Sk})")
+    if m.stride(-1) != 1 and Sk > 1:
+        m = m.contiguous()
+    sb = 0 if m.shape[0] == 1 else m.stride(0)
+    sh = 0 if m.shape[1] == 1 else m.stride(1)
+    sq = m.stride(2) if Sq > 1 else max(Sk, m.stride(2))
+    if sq < Sk:  # an expanded query dim: materialise, the kernel wants real rows
+        m = m.contiguous()
+        sb = 0 if m.shape[0] == 1 else m.stride(0)
+        sh = 0 if m.shape[1] == 1 else m.stride(1)
+        sq = m.stride(2)
+    return m, (sb, sh, sq)
+
+
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = False,
               scale: Optional[float] = None, window: Optional[Tuple[int, int]] = None,
-              alibi_slopes: Optional[torch.Tensor] = None, return_lse: bool = False):
+              alibi_slopes: Optional[torch.Tensor] = None, return_lse: bool = False,
+              attn_mask: Optional[torch.Tensor] = None):
     """softmax(scale * q k^T + bias) v; q (B,Sq,Hq,D), k/v (B,Sk,Hk,D), Hq % Hk == 0.
 
     Query head h reads kv head h // (Hq // Hk). window = (left, right) keeps keys with
-    -left <= j - i <= right. alibi_slopes (Hq,) adds -slope * |i - j|.
+    -left <= j - i <= right. alibi_slopes (Hq,) adds -slope * |i - j|. attn_mask is a dense
+    additive mask (Sq,Sk), (B,Sq,Sk), (B,1,Sq,Sk) or (B,Hq,Sq,Sk), float (added to the scaled
+    scores) or bool (True = hidden), broadcast by stride, never expanded.
     """
-    dev = _need_cuda(q, k, v, alibi_slopes)
+    dev = _need_cuda(q, k, v, alibi_slopes, attn_mask)
     if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError("attention needs q, k, v of one dtype, bfloat16 or float16")
     q, k, v = _bshd(q), _bshd(k), _bshd(v)
@@ -360,6 +394,18 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
     out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=dev)
     lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=dev) if return_lse else None
     ws = _workspace(dev)
+    if attn_mask is not None:
+        m, mstr = _dense_mask(attn_mask, B, Hq, Sq, Sk, q.dtype)
+        with torch.cuda.device(dev):
+            rc = _lib.load().trx_attn_fwd_mask(
+                _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), _ptr(slopes), _ptr(m), _code(m),
+                I64x3(*mstr), B, Sq, Sk, Hq, Hk, D, I64x3(*q.stride()[:3]),
+                I64x3(*k.stride()[:3]), I64x3(*v.stride()[:3]), I64x3(*out.stride()[:3]),
+                float(scale), int(bool(causal)), wl, wr, _code(q), _ptr(ws), ws.numel(),
+                _stream(dev))
+        _lib.check("trx_attn_fwd_mask", rc)
+        _count()
+        return (out, lse) if return_lse else out
     with torch.cuda.device(dev):
         rc = _lib.load().trx_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse),
                                       _ptr(slopes), B, Sq, Sk, Hq, Hk, D, I64x3(*q.stride()[:3]),
