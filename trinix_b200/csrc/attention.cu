@@ -338,7 +338,8 @@ __device__ __forceinline__ TileRange tile_range(const AttnParams& p, int row0) {
   return r;
 }
 
-template <int D, bool BF16>
+// BIAS: the instantiation that reads a dense additive mask; the other one carries none of it.
+template <int D, bool BF16, bool BIAS>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
     attn_fwd_kernel(const __grid_constant__ AttnParams p) {
   using L = AttnSmem<D>;
@@ -601,7 +602,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     const float sl2 = p.scale_log2;
     const float slope2 = p.slopes ? p.slopes[h] * 1.4426950408889634f : 0.0f;
     const bool has_alibi = p.slopes != nullptr;
-    const bool has_bias = p.bias_kind != 0;
+    constexpr bool has_bias = BIAS;
     // rows of the dense mask that this thread's two score rows read (valid rows only)
     const uint8_t* brow[2] = {nullptr, nullptr};
     if (has_bias) {
@@ -951,21 +952,28 @@ static int make_map(CUtensorMap* tm, const void* base, int is_bf16, int64_t D, i
   return r == CUDA_SUCCESS ? TRX_OK : TRX_ERR_CUDA;
 }
 
-template <int D, bool BF16>
-static int launch_attn(const AttnParams& p, cudaStream_t stream) {
+template <int D, bool BF16, bool BIAS>
+static int launch_attn_bias(const AttnParams& p, cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return TRX_ERR_CUDA;
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(attn_fwd_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(attn_fwd_kernel<D, BF16, BIAS>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
                              AttnSmem<D>::DYN_BYTES) != cudaSuccess)
       return TRX_ERR_CUDA;
     configured[dev] = true;
   }
   const int mblocks = (p.Sq + ATT_NQ * ATT_BM - 1) / (ATT_NQ * ATT_BM);
   dim3 grid(mblocks, p.Hq, p.B);
-  attn_fwd_kernel<D, BF16><<<grid, ATT_THREADS, AttnSmem<D>::DYN_BYTES, stream>>>(p);
+  attn_fwd_kernel<D, BF16, BIAS><<<grid, ATT_THREADS, AttnSmem<D>::DYN_BYTES, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? TRX_OK : TRX_ERR_CUDA;
+}
+
+template <int D, bool BF16>
+static int launch_attn(const AttnParams& p, cudaStream_t stream) {
+  return p.bias_kind != 0 ? launch_attn_bias<D, BF16, true>(p, stream)
+                          : launch_attn_bias<D, BF16, false>(p, stream);
 }
 
 }  // namespace trx
