@@ -137,3 +137,20 @@ def test_patched_reference_modules_if_installed(cuda):
         assert rel_err(FastSwiGLU(1024)(xg).cpu(), R.swiglu_ref(xg.cpu())) <= 1e-2
     finally:
         T.uninstall()
+
+
+def test_fused_rmsnorm_int8_module_equals_the_two_modules(cuda):
+    """fuse(FastRMSNorm, RowwiseInt8Quant) runs one kernel and returns exactly what the two
+    modules return one after the other."""
+    g = torch.Generator().manual_seed(5)
+    x = (torch.randn(3, 50, 4096, generator=g) * 2).bfloat16().to(cuda)
+    norm = T.FastRMSNorm(4096, eps=1e-6).to(cuda).bfloat16()
+    with torch.no_grad():
+        norm.weight.copy_(1 + 0.1 * torch.randn(4096, generator=g))
+    fused = T.fuse(norm, T.RowwiseInt8Quant())
+    before = T.ops.launch_count
+    codes, scales = fused(x)
+    assert T.ops.launch_count == before + 1
+    codes2, scales2 = T.RowwiseInt8Quant()(norm(x))
+    assert torch.equal(codes, codes2) and torch.equal(scales, scales2)
+    assert codes.shape == x.shape and scales.shape == x.shape[:-1]

@@ -151,11 +151,37 @@ def test_install_patches_the_reference_in_place():
             with torch.no_grad():
                 m.weight.copy_(G("rms_f32_w"))
                 torch.testing.assert_close(m(G("rms_f32_x")), G("rms_f32_y"), rtol=2e-6, atol=2e-6)
+            # the reference's own fuse() now knows the int8 pattern
+            ref_fused = trinix.fuse(RefFastRMSNorm(4096), T.RowwiseInt8Quant())
+            assert isinstance(ref_fused, T.FastFusedRMSNormInt8) and ref_fused.hidden_size == 4096
             # strict mode: the reference's silent-fallback warning is an error
             with pytest.raises(UserWarning):
                 warnings.warn("Triton attention kernel failed: x, falling back to PyTorch")
         finally:
             T.uninstall()
         assert RefRMS.__dict__["apply"] is before
+        import trinix.fusion as ref_fusion
+        assert (RefFastRMSNorm, T.RowwiseInt8Quant) not in ref_fusion._FUSION_REGISTRY
     finally:
         sys.path.remove(REFERENCE_DIR)
+
+
+def test_fuse_registry_mirrors_the_reference_contract():
+    """fuse(norm, quant) finds the fused module and shares the norm's weight; an unknown chain
+    warns and runs sequentially (trinix/fusion.py:31-77); fewer than two modules is an error."""
+    import warnings
+    import torch.nn as nn
+    norm = T.FastRMSNorm(4096, eps=1e-5)
+    fused = T.fuse(norm, T.RowwiseInt8Quant())
+    assert isinstance(fused, T.FastFusedRMSNormInt8)
+    assert fused.weight is norm.weight and fused.eps == 1e-5 and fused.hidden_size == 4096
+    with pytest.raises(ValueError):
+        T.fuse(norm)
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        seq = T.fuse(norm, nn.Identity())
+    assert isinstance(seq, nn.Sequential) and any("No fused kernel" in str(x.message) for x in w)
+    with pytest.raises(ValueError, match="last dimension"):
+        fused(torch.zeros(2, 8))
+    with pytest.raises(ValueError, match="CUDA"):   # no CPU path behind the fused module
+        fused(torch.zeros(2, 4096))

@@ -6,6 +6,7 @@ point (`functional.triton_attn_func`), mirror modules (`layers`) and `install()`
 patches an installed Trinix in place. CUDA tensors only; no fallback paths.
 """
 from .functional import flash_attn_func, triton_attn_func
+from .fusion import FastFusedRMSNormInt8, RowwiseInt8Quant, fuse, register_fusion
 from .install import install, uninstall
 from .kernels import (
     RowwiseInt8Kernel,

@@ -17,29 +17,19 @@
 
 namespace trx {
 
-// (threads per row, vectors per thread) for rows of up to 256 / 512 vectors (4096 bf16
-// columns sit in the second class). Few vectors per thread keep register pressure low enough
-// for 10+ CTAs per SM; the row then spans several warps and pays one barrier per reduction.
+// (threads per row, vectors per thread) for rows of up to 256 vectors. Few vectors per thread
+// keep register pressure low enough for many CTAs per SM; the row then spans several warps
+// and pays one barrier per reduction. Rows of up to 512 vectors (4096 bf16 columns, the
+// benchmark width) choose per op, see launch_row.
 #ifndef TRX_ROW256_TPR
 #define TRX_ROW256_TPR 64
 #define TRX_ROW256_VPT 4
 #endif
-#ifndef TRX_ROW512_TPR
-#define TRX_ROW512_TPR 128
-#define TRX_ROW512_VPT 4
-#endif
 
-// Minimum resident CTAs per SM asked of the compiler (caps registers per thread).
 // How many rows ahead of the one it is loading a CTA asks the copy engine to pull into L2
 // (one bulk-prefetch instruction per row, fire and forget). 0 = off.
 #ifndef TRX_ROW_L2_PREFETCH
 #define TRX_ROW_L2_PREFETCH 1
-#endif
-#ifndef TRX_ROW_MINBLOCKS
-#ifndef TRX_ROW_THREADS_PER_SM
-#define TRX_ROW_THREADS_PER_SM 1024
-#endif
-#define TRX_ROW_MINBLOCKS(TPR) ((TPR) > 32 ? ((TPR) <= 256 ? TRX_ROW_THREADS_PER_SM / (TPR) : 1) : 3)
 #endif
 
 enum RowOp {
@@ -58,6 +48,15 @@ __host__ __device__ constexpr bool op_has_quant(int op) {
   return op == OP_QUANT || op == OP_RMSNORM_QUANT || op == OP_RES_RMSNORM_QUANT;
 }
 __host__ __device__ constexpr bool op_has_res(int op) { return op == OP_RES_RMSNORM || op == OP_RES_RMSNORM_QUANT; }
+// Minimum resident CTAs per SM asked of the compiler (caps registers per thread): a thread
+// budget per SM that was measured per family, divided by the CTA size.
+__host__ __device__ constexpr int row_min_blocks(int op, int tpr, int vpt) {
+  if (tpr <= 32) return 3;                      // 256-thread CTAs, 8 rows each
+  if (tpr > 256) return 1;
+  if (op_has_res(op)) return 768 / tpr;         // two streams + fp32 copies: more registers
+  if (tpr == 64 && vpt == 8) return 640 / tpr;  // 8 vectors per thread in flight
+  return 1024 / tpr;
+}
 
 struct RowParamsBase {
   const void* x;
@@ -129,9 +128,7 @@ __device__ __forceinline__ float rsqrt_approx(float v) {
 // CTA, so no vector of any thread is padding. The guards disappear, and with them some thirty
 // branches per warp and row that kept the four vectors of a thread from being scheduled together.
 template <int OP, typename T, int TPR, int VPT, bool FULL>
-__global__ void __launch_bounds__((TPR > 32 ? TPR : 256),
-                                  (op_has_res(OP) && TPR > 32 && TPR <= 256) ? 768 / TPR
-                                                                               : TRX_ROW_MINBLOCKS(TPR))
+__global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR, VPT))
     row_kernel(const RowParamsBase p, const ResArg<OP> rp) {
   using P = Pack<T>;
   constexpr int VEC = P::VEC;
@@ -549,10 +546,7 @@ static int launch_cfg_full(const RowParams& p, cudaStream_t stream) {
 template <int OP, typename T, int TPR, int VPT>
 static int launch_cfg(const RowParams& p, cudaStream_t stream) {
   constexpr int ROWS_PER_CTA = (TPR > 32 ? TPR : 256) / TPR;
-#ifndef TRX_ROW_FULL_MAX_VPT
-#define TRX_ROW_FULL_MAX_VPT 4
-#endif
-  if constexpr (VPT <= TRX_ROW_FULL_MAX_VPT) {  // built where rows of that exact width matter
+  if constexpr (VPT <= 4 || (TPR == 64 && VPT == 8)) {  // built where that exact width matters
     if (p.C / Pack<T>::VEC == TPR * VPT && p.R % ROWS_PER_CTA == 0)
       return launch_cfg_full<OP, T, TPR, VPT, true>(p, stream);
   }
@@ -584,10 +578,14 @@ static int launch_row(const RowParams& p, cudaStream_t stream) {
     if (nvec <= 128) return launch_cfg<OP, T, 32, 4>(p, stream);
     if (nvec <= 256) return launch_cfg<OP, T, TRX_ROW256_TPR, TRX_ROW256_VPT>(p, stream);
     if (nvec <= 512) {
-      // two input streams per row: 256 threads x 2 vectors measured 93-95 % of the copy rate,
-      // 128 x 4 (best for the single-stream ops) 86 %
+      // Measured on 32768 x 4096 bf16, per family: two input streams per row (residual forms)
+      // 256 threads x 2 vectors (93-95 % of the copy rate against 86 % for 128 x 4); the
+      // quantiser 64 x 8 at 10 CTAs per SM (+5 % over 128 x 4); the norms 128 x 4. RMSNorm ->
+      // int8 stays on RMSNorm's configuration although 64 x 8 would gain it 2 %: the two must
+      // sum the squares in the same order to stay equal bit for bit.
       if constexpr (op_has_res(OP)) return launch_cfg<OP, T, 256, 2>(p, stream);
-      else return launch_cfg<OP, T, TRX_ROW512_TPR, TRX_ROW512_VPT>(p, stream);
+      else if constexpr (OP == OP_QUANT) return launch_cfg<OP, T, 64, 8>(p, stream);
+      else return launch_cfg<OP, T, 128, 4>(p, stream);
     }
     if (nvec <= 1024) return launch_cfg<OP, T, 256, 4>(p, stream);
     if (nvec <= 2048) return launch_cfg<OP, T, 512, 4>(p, stream);

@@ -19,6 +19,7 @@ from . import functional
 from .kernels import KERNEL_CLASSES
 
 _saved: Dict[Tuple[object, str], object] = {}
+_saved_patterns: list = []  # (registry dict, pattern key, previous factory or None)
 _FALLBACK_WARNING = "Triton attention kernel failed"
 
 
@@ -56,6 +57,16 @@ def install(strict: bool = True):
         _rebind(attn_pkg, "triton_attn_func", functional.triton_attn_func)
     if hasattr(trinix, "triton_attn_func"):
         _rebind(trinix, "triton_attn_func", functional.triton_attn_func)
+    # trinix.fuse(FastRMSNorm(...), RowwiseInt8Quant()) -> the fused RMSNorm -> int8 kernel
+    try:
+        fusion_mod = importlib.import_module("trinix.fusion")
+        from . import fusion as ours_fusion
+        key = (trinix.FastRMSNorm, ours_fusion.RowwiseInt8Quant)
+        _saved_patterns.append((fusion_mod._FUSION_REGISTRY, key,
+                                fusion_mod._FUSION_REGISTRY.get(key)))
+        ours_fusion.register_with_trinix(fusion_mod, trinix.FastRMSNorm)
+    except (ImportError, AttributeError):
+        pass  # a Trinix without the fusion registry: nothing to add
     if strict:
         warnings.filterwarnings("error", message=f".*{_FALLBACK_WARNING}.*")
     return trinix
@@ -72,4 +83,10 @@ def uninstall() -> None:
         else:
             setattr(obj, name, old)
     _saved.clear()
+    for registry, key, old in _saved_patterns:
+        if old is None:
+            registry.pop(key, None)
+        else:
+            registry[key] = old
+    _saved_patterns.clear()
     warnings.filterwarnings("default", message=f".*{_FALLBACK_WARNING}.*")
