@@ -41,7 +41,7 @@ BYTES_STEP = BYTES_QUANT + BYTES_DEQUANT + BYTES_FUSED
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused RMSNorm->int8 kernel
 # on this shape, from an ncu capture of `bench.py --profile-case int8`
-FUSED_DRAM_TRAFFIC = 268_472_832 + 97_137_664
+FUSED_DRAM_TRAFFIC = 268_475_392 + 100_498_432
 
 
 def peaks():
@@ -356,6 +356,7 @@ def profile_case(name: str):
             ops.rmsnorm_quantize(acts[i % 2], w, 1e-6)
             c, sc = ops.quantize_rowwise(xq[i % 3])
             ops.dequantize_rowwise(c, sc, torch.bfloat16)
+            ops.residual_rmsnorm_quantize(acts[i % 2], acts[(i + 1) % 2], w, 1e-6, True)
     elif name == "stream":
         acts = [rnd(ACT_ROWS, ACT_SHAPE[2]) for _ in range(2)]
         w = torch.ones(ACT_SHAPE[2], device=device, dtype=torch.bfloat16)
