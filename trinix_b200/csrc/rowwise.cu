@@ -579,12 +579,12 @@ static int launch_row(const RowParams& p, cudaStream_t stream) {
     if (nvec <= 256) return launch_cfg<OP, T, TRX_ROW256_TPR, TRX_ROW256_VPT>(p, stream);
     if (nvec <= 512) {
       // Measured on 32768 x 4096 bf16, per family: two input streams per row (residual forms)
-      // 256 threads x 2 vectors (93-95 % of the copy rate against 86 % for 128 x 4); the
-      // quantiser 64 x 8 at 10 CTAs per SM (+5 % over 128 x 4); the norms 128 x 4. RMSNorm ->
-      // int8 stays on RMSNorm's configuration although 64 x 8 would gain it 2 %: the two must
-      // sum the squares in the same order to stay equal bit for bit.
+      // 256 threads x 2 vectors (93-95 % of the copy rate against 86 % for 128 x 4); the int8
+      // encoders 64 x 8 at 10 CTAs per SM (+2-5 % over 128 x 4); LayerNorm 128 x 4. RMSNorm
+      // follows RMSNorm -> int8 (which costs it 1 %): the two must sum the squares in the same
+      // order to stay equal bit for bit.
       if constexpr (op_has_res(OP)) return launch_cfg<OP, T, 256, 2>(p, stream);
-      else if constexpr (OP == OP_QUANT) return launch_cfg<OP, T, 64, 8>(p, stream);
+      else if constexpr (op_has_quant(OP) || OP == OP_RMSNORM) return launch_cfg<OP, T, 64, 8>(p, stream);
       else return launch_cfg<OP, T, 128, 4>(p, stream);
     }
     if (nvec <= 1024) return launch_cfg<OP, T, 256, 4>(p, stream);
