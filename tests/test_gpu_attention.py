@@ -236,3 +236,29 @@ def test_dense_mask_rejects_bad_shapes(cuda):
         T.triton_attn_func(q, k, v, attn_mask=torch.zeros(3, 128, 128, device=cuda))
     with pytest.raises(ValueError):
         T.triton_attn_func(q, k, v, attn_mask=torch.zeros(1, 1, 1, 128, 128, device=cuda))
+
+
+def test_launch_after_recorded_failure_is_skipped_until_cleared(cuda):
+    """A non-zero status word (a bounded wait gave up in some earlier launch) makes every later
+    launch return at once, its on-chip resources released; reading the word clears it and the
+    kernel works again."""
+    from trinix_b200 import ops
+    q, k, v = (t.to(cuda) for t in _qkv(1, 512, 512, 4, 2, 128, seed=21))
+    good = T.attention(q, k, v, causal=True)
+    assert T.attention_status(cuda) == 0
+    ops._workspace(cuda)[:4].view(torch.int32).fill_(4)     # as if a softmax wait had run out
+    for _ in range(3):                                       # skipped launches, several in a row
+        T.attention(q, k, v, causal=True)
+    torch.cuda.synchronize(cuda)
+    assert T.attention_status(cuda) == 4                     # reported once, then cleared
+    assert T.attention_status(cuda) == 0
+    again = T.attention(q, k, v, causal=True)
+    assert torch.equal(again, good)
+
+
+@pytest.mark.parametrize("Sq,Sk", [(1, 1000), (1, 128), (7, 2049), (130, 64)])
+def test_decode_shapes_kv_longer_or_shorter_than_q(cuda, Sq, Sk):
+    """KV-cache decode shapes (grouped_query_attention.py:179-187 concatenates past keys, so
+    Sk > Sq, down to a single query row), GQA heads, no mask."""
+    q, k, v = _qkv(2, Sq, Sk, 8, 2, 128, seed=Sq * 7 + Sk)
+    _check(cuda, q, k, v)

@@ -385,12 +385,28 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   // A launch that follows a recorded failure does no work: the host must read and clear
   // the status word first.
   __shared__ int skip_launch;
-  if (threadIdx.x == 0)
-    skip_launch = (*reinterpret_cast<volatile unsigned int*>(p.status) != 0u) ? 1 : 0;
-  __syncthreads();
-  if (skip_launch) return;
 
-  if (threadIdx.x == 0) {
+  // One K or V tile into ring stage fill % STAGES (K and V tiles alternate: even fills are K).
+  auto issue_fill = [&](int fill) {
+    const int s = fill % ATT_STAGES;
+    const int j = JLO + fill / 2;
+    const bool is_k = (fill & 1) == 0;
+    mbar_expect_tx(bar(B_KVFULL + s), L::TILE_BYTES);
+    fills_issued[s] = fill / ATT_STAGES + 1;
+    const CUtensorMap* tm = is_k ? &p.tm_k : &p.tm_v;
+    const int hh = h / (is_k ? p.k_hdiv : p.v_hdiv);
+    const int bb = b * (is_k ? p.k_bmul : p.v_bmul);
+#pragma unroll
+    for (int c = 0; c < L::CHUNKS; ++c)
+      tma_load_4d(sbase + L::KV_OFF + s * L::TILE_BYTES + c * L::CHUNK_BYTES, tm,
+                  bar(B_KVFULL + s), c * 64, j * ATT_BN, hh, bb);
+  };
+  // The producer warp's first lane sets up the barriers and starts the Q and first K/V copies
+  // before the CTA-wide sync, so that they run under the TMEM allocation and the sync itself.
+  if (warp == ATT_SM_WARPS && lane == 0) {
+    skip_launch = (*reinterpret_cast<volatile unsigned int*>(p.status) != 0u) ? 1 : 0;
+  }
+  if (warp == ATT_SM_WARPS && lane == 0 && !skip_launch) {
     mbar_init(bar(B_QFULL + 0), 1);
     mbar_init(bar(B_QFULL + 1), 1);
     for (int s = 0; s < ATT_STAGES; ++s) {
@@ -408,22 +424,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(tmem_holder)),
-                 "r"(512u)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_holder;
-
-  if (warp == ATT_SM_WARPS) {
-    // =========================== TMA producer =========================================
-    if (lane == 0 && JHI > JLO) {
+    if (JHI > JLO) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_q) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_k) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&p.tm_v) : "memory");
@@ -437,26 +438,41 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                         bar(B_QFULL + t), c * 64, m0 + t * ATT_BM, h, b);
         }
       }
-      const int hk = h / p.k_hdiv, hv = h / p.v_hdiv;
-      const int bk = b * p.k_bmul, bv = b * p.v_bmul;
-      int fill = 0;
+      // the ring is empty: its first round of fills waits for nobody
+      const int first_round = min(ATT_STAGES, 2 * (JHI - JLO));
+      for (int fill = 0; fill < first_round; ++fill) issue_fill(fill);
+    }
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_holder)),
+                 "r"(512u)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  if (skip_launch) {  // nothing was started: give the TMEM columns back and leave
+    if (warp == 0)
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(512u)
+                   : "memory");
+    return;
+  }
+
+  if (warp == ATT_SM_WARPS) {
+    // =========================== TMA producer =========================================
+    if (lane == 0 && JHI > JLO) {
+      // Q and the first round of the ring were issued before the CTA-wide sync
+      const int total = 2 * (JHI - JLO);
       bool ok = true;
-      for (int j = JLO; j < JHI && ok; ++j) {
-#pragma unroll
-        for (int kv = 0; kv < 2; ++kv, ++fill) {
-          const int s = fill % ATT_STAGES;
-          const uint32_t par = ((fill / ATT_STAGES) & 1) ^ 1;
-          ok = mbar_wait(bar(B_KVEMPTY + s), par, abort_flag, p.status, ATT_ST_PRODUCER);
-          if (!ok) break;
-          mbar_expect_tx(bar(B_KVFULL + s), L::TILE_BYTES);
-          fills_issued[s] = fill / ATT_STAGES + 1;
-          const CUtensorMap* tm = kv == 0 ? &p.tm_k : &p.tm_v;
-#pragma unroll
-          for (int c = 0; c < L::CHUNKS; ++c)
-            tma_load_4d(sbase + L::KV_OFF + s * L::TILE_BYTES + c * L::CHUNK_BYTES, tm,
-                        bar(B_KVFULL + s), c * 64, j * ATT_BN, kv == 0 ? hk : hv,
-                        kv == 0 ? bk : bv);
-        }
+      for (int fill = ATT_STAGES; fill < total && ok; ++fill) {
+        const uint32_t par = ((fill / ATT_STAGES) & 1) ^ 1;
+        ok = mbar_wait(bar(B_KVEMPTY + fill % ATT_STAGES), par, abort_flag, p.status,
+                       ATT_ST_PRODUCER);
+        if (ok) issue_fill(fill);
       }
     }
   } else if (warp == ATT_SM_WARPS + 1) {
