@@ -251,13 +251,15 @@ def bench_ops(device, pk):
 def bench_layer(device):
     """Llama-2-7B-shaped decoder layer forward on one GPU's shard [4, 2048, 4096]: int8 weight
     store dequantised to bf16 by the kernel each forward, cuBLAS GEMMs, kernels of this package
-    for norms / RoPE / attention / SwiGLU."""
+    for norms (the second one fused with the residual add) / RoPE / attention / SwiGLU."""
     import torch.nn.functional as F
     import trinix_b200 as T
     E, Hq, Hkv, FF, B, S = 4096, 32, 8, 11008, 4, 2048
     g = torch.Generator(device=device).manual_seed(0)
+    # up and gate projections stored as one matrix: one GEMM writes FastSwiGLU's concatenated
+    # [up, gate] input directly
     shapes = {"wq": (E, E), "wk": (Hkv * 128, E), "wv": (Hkv * 128, E), "wo": (E, E),
-              "w_gate": (FF, E), "w_up": (FF, E), "w_down": (E, FF)}
+              "w_up_gate": (2 * FF, E), "w_down": (E, FF)}
     store = {n: T.quantize_rowwise((0.02 * torch.randn(*s, generator=g, device=device)).bfloat16())
              for n, s in shapes.items()}
     attn = T.FastGroupedQueryAttention(E, Hq, Hkv, bias=False, kernel_type="triton", causal=True,
@@ -272,9 +274,10 @@ def bench_layer(device):
         w = {n: T.dequantize_rowwise(c, s, torch.bfloat16) for n, (c, s) in store.items()}
         attn.q_proj.weight.data, attn.k_proj.weight.data = w["wq"], w["wk"]
         attn.v_proj.weight.data, attn.o_proj.weight.data = w["wv"], w["wo"]
-        h = x + attn(n1(x))[0]
-        n = n2(h)
-        ff = act(torch.cat([F.linear(n, w["w_up"]), F.linear(n, w["w_gate"])], dim=-1))
+        a = attn(n1(x))[0]
+        # residual add and the second norm in one pass: n = RMSNorm(a + x), h = a + x
+        n, h = T.residual_rmsnorm(a, x, n2.weight, n2.eps, return_sum=True)
+        ff = act(F.linear(n, w["w_up_gate"]))
         return h + F.linear(ff, w["w_down"])
 
     ms = event_ms([forward], warmup=2, iters=5)
