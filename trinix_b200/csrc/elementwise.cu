@@ -2,11 +2,11 @@
 // in one launch) and per-row int8 dequantisation.
 //
 // All three are pure HBM streams. Each thread moves 16-byte vectors with
-// streaming loads/stores and keeps several independent loads in flight (four / eight
-// rows per thread for GLU / dequant; the two halves of a head vector plus the
-// table entries for RoPE). Grids are 2-D (column-vector block, row block) so no
-// thread ever divides to find its row. Shapes or pointers that do not fit the
-// vector path take a scalar kernel.
+// streaming loads/stores; GLU keeps four rows (eight loads) in flight per thread, RoPE the
+// two halves of four head vectors, the dequantiser one light row block per thread on a
+// very large grid. Grids are 2-D (column-vector block, row block) so no thread ever
+// divides to find its row. Shapes or pointers that do not fit the vector path take a
+// scalar kernel.
 #include "common.cuh"
 
 namespace trx {

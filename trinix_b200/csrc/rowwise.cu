@@ -1,16 +1,18 @@
-// Row kernels: RMSNorm, LayerNorm, per-row int8 quantise, fused RMSNorm -> int8.
+// Row kernels: RMSNorm, LayerNorm, per-row int8 quantise, fused RMSNorm -> int8, and the
+// residual forms RMSNorm(x + r) and RMSNorm(x + r) -> int8.
 //
-// One skeleton serves the four ops. A row is read from HBM exactly once with
+// One skeleton serves the six ops. A row is read from HBM exactly once with
 // 128-bit streaming loads and then lives in registers (VPT 16-byte vectors per
 // thread, TPR threads per row); statistics are reduced with warp shuffles
 // (plus one shared-memory hop when a row spans more than one warp), and the
 // result is produced from the registers — the row is never re-read.
 //   TPR == 32 : one warp per row, 8 rows per 256-thread CTA, no barriers at all (short rows).
 //   TPR  > 32 : one CTA of TPR threads per row, few vectors per thread.
-// CTAs are persistent: the grid is sized to what the 148 SMs can hold and
-// strides over the rows. Rows that do not fit the vector path (columns not a
-// multiple of the vector width, unaligned pointers, more than 16384 vectors)
-// take a scalar multi-pass kernel, so nothing is ever truncated.
+// The grid is several resident waves of CTAs, each striding over a few rows (see
+// launch_cfg_full). Rows of exactly TPR * VPT vectors run a specialisation without guards.
+// Rows that do not fit the vector path (columns not a multiple of the vector width,
+// unaligned pointers, more than 16384 vectors) take a scalar multi-pass kernel, so nothing
+// is ever truncated.
 #include <type_traits>
 
 #include "common.cuh"
