@@ -6,7 +6,7 @@ import torch
 
 import trinix_b200 as T
 from oracle import int8_numpy as N, reference_port as R
-from tests.util import Golden, bf16_ulps, outlier_matrix, rel_err
+from tests.util import Golden, assert_norm_close, bf16_ulps, outlier_matrix, rel_err
 
 pytestmark = pytest.mark.gpu
 G = Golden()
@@ -243,3 +243,37 @@ def test_residual_rmsnorm_quant_equals_unfused_bit_exact(cuda):
         assert torch.equal(codes, c2) and torch.equal(scales.view(torch.int32), sc2.view(torch.int32))
         assert torch.equal(s, s2)
         _assert_quant_exact(y.cpu(), codes, scales)  # oracle quantiser on the kernel's norm output
+
+
+@pytest.mark.parametrize("nvec", [32, 64, 128, 256, 512, 1024, 2048, 4096])
+@pytest.mark.parametrize("rows", [1, 8, 19, 304])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_every_op_on_exact_width_rows(cuda, nvec, rows, dtype):
+    """Rows of exactly threads x vectors width take the guard-free specialisation of every
+    configuration (one warp per row up to 1024 threads per row); row counts that are and are
+    not a multiple of the rows per CTA. All six ops against the oracle."""
+    cols = nvec * (8 if dtype == torch.bfloat16 else 4)
+    g = torch.Generator().manual_seed(nvec * 7 + rows)
+    x = torch.randn(rows, cols, generator=g).to(dtype)
+    r = torch.randn(rows, cols, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype)
+    b = (0.1 * torch.randn(cols, generator=g)).to(dtype)
+    xc, rc, wc, bc = x.to(cuda), r.to(cuda), w.to(cuda), b.to(cuda)
+    assert_norm_close(T.ops.rmsnorm(xc, wc, 1e-6).cpu(), R.rmsnorm_ref(x, w, 1e-6))
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert rel_err(T.ops.layernorm(xc, wc, bc, 1e-5).cpu(), R.layernorm_ref(x, w, b, 1e-5)) <= tol
+    codes, scales = T.quantize_rowwise(xc)
+    _assert_quant_exact(x, codes, scales)
+    # fused == unfused, bit for bit, and the oracle's quantiser on the kernel's norm agrees
+    y = T.ops.rmsnorm(xc, wc, 1e-6)
+    fc, fs = T.rmsnorm_quantize(xc, wc, 1e-6)
+    uc, us = T.quantize_rowwise(y)
+    assert torch.equal(fc, uc) and torch.equal(fs, us)
+    _assert_quant_exact(y.cpu(), fc, fs)
+    if nvec <= 4096 // (2 if dtype == torch.bfloat16 else 1):
+        yr, sr = T.ops.residual_rmsnorm(xc, rc, wc, 1e-6, return_sum=True)
+        assert_norm_close(yr.cpu(), R.residual_rmsnorm_ref(x, r, w, 1e-6))
+        assert rel_err(sr.cpu(), (x.float() + r.float()).to(dtype)) <= (1e-6 if dtype == torch.float32 else 4e-3)
+        qc, qs, _ = T.ops.residual_rmsnorm_quantize(xc, rc, wc, 1e-6, return_sum=True)
+        uc2, us2 = T.quantize_rowwise(yr)
+        assert torch.equal(qc, uc2) and torch.equal(qs, us2)
