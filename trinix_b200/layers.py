@@ -226,6 +226,7 @@ class FastRoPEPositionEmbedding(nn.Module):
         self.use_triton = use_triton
         inv_freq = 1.0 / base ** (torch.arange(0, dim, 2).float() / dim)
         self.register_buffer("inv_freq", inv_freq, persistent=False)
+        self._table_key, self._tables = None, None
 
     def forward(self, x: torch.Tensor, seq_len: Optional[int] = None):
         """(cos, sin) of shape (seq_len, dim) in x's dtype. The angles are always built in
@@ -234,12 +235,18 @@ class FastRoPEPositionEmbedding(nn.Module):
         onto each other); this mirror keeps the buffer for state-dict compatibility only."""
         if seq_len is None:
             seq_len = x.shape[-2]
-        inv_freq = 1.0 / self.base ** (
-            torch.arange(0, self.dim, 2, device=x.device, dtype=torch.float32) / self.dim)
-        pos = torch.arange(seq_len, device=x.device, dtype=torch.float32)
-        angles = torch.outer(pos, inv_freq)
-        table = torch.cat((angles, angles), dim=-1)
-        return table.cos().to(x.dtype), table.sin().to(x.dtype)
+        # the tables depend on (seq_len, device, dtype) only: the last pair is kept, which saves
+        # a dozen small launches per forward in a decoder stack
+        key = (int(seq_len), x.device, x.dtype)
+        if self._table_key != key:
+            inv_freq = 1.0 / self.base ** (
+                torch.arange(0, self.dim, 2, device=x.device, dtype=torch.float32) / self.dim)
+            pos = torch.arange(seq_len, device=x.device, dtype=torch.float32)
+            angles = torch.outer(pos, inv_freq)
+            table = torch.cat((angles, angles), dim=-1)
+            self._tables = (table.cos().to(x.dtype), table.sin().to(x.dtype))
+            self._table_key = key
+        return self._tables
 
     @staticmethod
     def _rotate_half(x: torch.Tensor) -> torch.Tensor:
