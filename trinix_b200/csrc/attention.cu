@@ -652,7 +652,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       // t = s + (sgn*slope2/sl2)*c, and the per-tile, per-row constant `off` below.
       int alibi_sgn = 0;
       if (has_alibi) {
-        if (c0 + ATT_BN - 1 <= row0) alibi_sgn = 1;   // every key at or before every query
+        // under a causal mask (or a window that ends at the query) every VISIBLE key is at or
+        // before its query, on the diagonal tile too; hidden keys are masked anyway
+        if (p.causal || p.win_right == 0 || c0 + ATT_BN - 1 <= row0) alibi_sgn = 1;
         else if (c0 >= row1) alibi_sgn = -1;          // every key at or after every query
       }
       // general path: a tile that straddles the diagonal under ALiBi, or a non-positive scale
@@ -710,12 +712,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 #pragma unroll
           for (int hr = 0; hr < 2; ++hr)
             off[hr] = sk * static_cast<float>(c0 + 2 * q4 - row_g[hr]);
+          // + kc * (8g + e), as packed adds of a running (column, column + 1) pair
+          float2 cp = make_float2(0.0f, kc);
+          const float2 step = make_float2(8.0f * kc, 8.0f * kc);
 #pragma unroll
           for (int g = 0; g < 16; ++g) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              sr[4 * g + k] = __float_as_uint(
-                  fmaf(kc, static_cast<float>(8 * g + (k & 1)), __uint_as_float(sr[4 * g + k])));
+            for (int hr = 0; hr < 2; ++hr) {
+              const float2 v = add2(make_float2(__uint_as_float(sr[4 * g + 2 * hr]),
+                                                __uint_as_float(sr[4 * g + 2 * hr + 1])), cp);
+              sr[4 * g + 2 * hr] = __float_as_uint(v.x);
+              sr[4 * g + 2 * hr + 1] = __float_as_uint(v.y);
+            }
+            cp = add2(cp, step);
           }
         }
 #pragma unroll
