@@ -695,14 +695,33 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         if (need_mask) {
           // boundary tile: hide keys outside [lo, hi] in the raw domain (sl2 > 0 keeps -inf
           // at -inf), then continue on the fast path
+          // a tile is cut by the upper bound (diagonal), by the lower one (left edge of a
+          // window), seldom by both: one comparison per score where one is enough
+          const bool cut_hi = c0 + ATT_BN - 1 > hi_min, cut_lo = c0 < lo_max;
 #pragma unroll
           for (int hr = 0; hr < 2; ++hr) {
             const int lo_c = lo_i[hr] - c0 - 2 * q4, hi_c = hi_i[hr] - c0 - 2 * q4;
+            if (cut_hi && !cut_lo) {
 #pragma unroll
-            for (int g = 0; g < 16; ++g) {
+              for (int g = 0; g < 16; ++g) {
 #pragma unroll
-              for (int e = 0; e < 2; ++e)
-                if (8 * g + e < lo_c || 8 * g + e > hi_c) sr[4 * g + 2 * hr + e] = 0xff800000u;
+                for (int e = 0; e < 2; ++e)
+                  if (8 * g + e > hi_c) sr[4 * g + 2 * hr + e] = 0xff800000u;
+              }
+            } else if (cut_lo && !cut_hi) {
+#pragma unroll
+              for (int g = 0; g < 16; ++g) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e)
+                  if (8 * g + e < lo_c) sr[4 * g + 2 * hr + e] = 0xff800000u;
+              }
+            } else {
+#pragma unroll
+              for (int g = 0; g < 16; ++g) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e)
+                  if (8 * g + e < lo_c || 8 * g + e > hi_c) sr[4 * g + 2 * hr + e] = 0xff800000u;
+              }
             }
           }
         }
