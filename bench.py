@@ -41,7 +41,7 @@ BYTES_STEP = BYTES_QUANT + BYTES_DEQUANT + BYTES_FUSED
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the fused RMSNorm->int8 kernel
 # on this shape, from an ncu capture of `bench.py --profile-case int8`
-FUSED_DRAM_TRAFFIC = 268_475_392 + 100_498_432
+FUSED_DRAM_TRAFFIC = 268_547_072 + 98_899_712
 
 
 def peaks():
