@@ -199,6 +199,14 @@ def bench_ops(device, pk):
         [lambda a=a: ops.layernorm(a, w, b, 1e-5) for a in acts])
     hbm("rmsnorm_quant_i8_32768x4096", BYTES_FUSED,
         [lambda a=a: ops.rmsnorm_quantize(a, w, 1e-6) for a in acts])
+    # residual forms (the step either side of the norm in a decoder layer), new residual stream
+    # written: 2 reads + 2 writes of 2 bytes (8C), or 2 reads + 1 write + codes (7C + 4)
+    hbm("residual_rmsnorm_sum_bf16_32768x4096", R_ * C_ * 8 + 2 * C_,
+        [lambda a=a, r=r: ops.residual_rmsnorm(a, r, w, 1e-6, True)
+         for a, r in ((acts[0], acts[1]), (acts[1], acts[0]))])
+    hbm("residual_rmsnorm_quant_sum_i8_32768x4096", R_ * C_ * 7 + 4 * R_ + 2 * C_,
+        [lambda a=a, r=r: ops.residual_rmsnorm_quantize(a, r, w, 1e-6, True)
+         for a, r in ((acts[0], acts[1]), (acts[1], acts[0]))])
     xs = [rnd(*QUANT_SHAPE) for _ in range(6)]  # 6 x (64 + 32) MB
     hbm("quant_i8_8192x4096", BYTES_QUANT, [lambda x=x: ops.quantize_rowwise(x) for x in xs])
     cs = [ops.quantize_rowwise(x) for x in xs]
