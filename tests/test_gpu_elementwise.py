@@ -104,3 +104,38 @@ def test_rope_strided_views_from_fused_qkv(cuda):
     assert not dq.is_contiguous()
     qo, ko = T.rope(dq, dk, cos.to(cuda), sin.to(cuda))
     assert torch.equal(qo.cpu(), rq.bfloat16()) and torch.equal(ko.cpu(), rk.bfloat16())
+
+
+def test_empty_inputs_every_op(cuda):
+    """Zero rows / tokens / queries: every entry point returns an empty result of the right
+    shape and dtype without launching anything."""
+    from trinix_b200 import ops
+    w = torch.ones(4096, device=cuda, dtype=torch.bfloat16)
+    x0 = torch.empty(0, 4096, device=cuda, dtype=torch.bfloat16)
+    before = ops.launch_count
+    assert T.ops.rmsnorm(x0, w, 1e-6).shape == (0, 4096)
+    assert T.ops.layernorm(x0, w, w, 1e-5).shape == (0, 4096)
+    c, s = T.quantize_rowwise(x0)
+    assert c.shape == (0, 4096) and c.dtype == torch.int8 and s.shape == (0,)
+    assert T.dequantize_rowwise(c, s, torch.bfloat16).shape == (0, 4096)
+    c, s = T.rmsnorm_quantize(x0, w, 1e-6)
+    assert c.shape == (0, 4096) and s.shape == (0,)
+    y, h = T.ops.residual_rmsnorm(x0, x0, w, 1e-6, return_sum=True)
+    assert y.shape == (0, 4096) and h.shape == (0, 4096)
+    assert T.ops.glu(torch.empty(0, 2 * 512, device=cuda, dtype=torch.bfloat16), "swiglu").shape == (0, 512)
+    q0 = torch.empty(0, 16, 4, 128, device=cuda, dtype=torch.bfloat16)
+    cos = torch.ones(16, 128, device=cuda)
+    qo, ko = T.ops.rope(q0, q0, cos, cos)
+    assert qo.shape == q0.shape and ko.shape == q0.shape
+    assert T.attention(q0, q0, q0, causal=True).shape == q0.shape
+    qz = torch.empty(2, 0, 4, 128, device=cuda, dtype=torch.bfloat16)      # no queries
+    kz = torch.randn(2, 64, 4, 128, device=cuda).bfloat16()
+    assert T.attention(qz, kz, kz).shape == qz.shape
+    torch.cuda.synchronize(cuda)
+    assert T.attention_status(cuda) == 0
+    # no keys at all: every row's softmax is empty, the output is defined as 0
+    qn = torch.randn(1, 130, 2, 128, device=cuda).bfloat16()
+    kn = torch.empty(1, 0, 2, 128, device=cuda, dtype=torch.bfloat16)
+    out = T.attention(qn, kn, kn)
+    assert out.shape == qn.shape and float(out.float().abs().max()) == 0.0
+    assert ops.launch_count >= before
