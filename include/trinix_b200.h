@@ -44,6 +44,13 @@ typedef enum trx_glu_act {
   TRX_GLU_REGLU = 2       /* up * max(gate, 0) */
 } trx_glu_act;
 
+/* Activation fused behind RMSNorm (trx_rmsnorm_act_fwd). */
+typedef enum trx_row_act {
+  TRX_ACT_MISH = 0,         /* n * tanh(softplus(n)) */
+  TRX_ACT_QUICKGELU = 1,    /* n * sigmoid(1.702 n) */
+  TRX_ACT_SQUARED_RELU = 2  /* max(n, 0)^2 */
+} trx_row_act;
+
 /* ABI version of the loaded library (TRX_ABI_VERSION at build time). */
 int trx_version(void);
 
@@ -105,6 +112,20 @@ int trx_dequant_rowwise_i8(const int8_t* codes, const float* scales, void* y, in
 int trx_rmsnorm_quant_i8(const void* x, const void* w, int8_t* codes, float* scales, int64_t R,
                          int64_t C, int64_t x_row_stride, int64_t codes_row_stride, float eps,
                          int x_dtype, int w_dtype, void* stream);
+
+/*
+ * act(RMSNorm(x)): n = round(w * round(x * rstd)) as trx_rmsnorm_fwd computes it (the product is
+ * rounded to the activation dtype only when w has that dtype; any other w dtype leaves it in
+ * fp32, PyTorch's promotion), then y = round(act(n)), act one of TRX_ACT_*. One pass over HBM
+ * instead of two.
+ * Follows FastFusedRMSNormActivation._pytorch_forward,
+ * trinix/layers/fused/rmsnorm_activation.py:72-86; replaces
+ * TritonFusedRMSNormActivationKernel.apply, trinix/kernels/fused/rmsnorm_activation_kernel.py
+ * (kernel :9-77).
+ */
+int trx_rmsnorm_act_fwd(const void* x, const void* w, void* y, int64_t R, int64_t C,
+                        int64_t x_row_stride, int64_t y_row_stride, float eps, int act,
+                        int x_dtype, int w_dtype, void* stream);
 
 /*
  * Fused residual add + RMSNorm: s = float(x) + float(residual) (kept in fp32 on chip),

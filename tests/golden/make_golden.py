@@ -27,6 +27,7 @@ from trinix.layers.embeddings.rope import FastRoPEPositionEmbedding  # noqa: E40
 from trinix.layers.norm.layernorm import FastLayerNorm  # noqa: E402
 from trinix.layers.norm.rmsnorm import FastRMSNorm  # noqa: E402
 from trinix.layers.fused.residual_rmsnorm import FastFusedResidualRMSNorm  # noqa: E402
+from trinix.layers.fused.rmsnorm_activation import FastFusedRMSNormActivation  # noqa: E402
 
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz")
 vec = {}
@@ -130,6 +131,20 @@ with torch.no_grad():
     for n in ("q_proj", "k_proj", "v_proj", "o_proj"):
         put(f"gqa_{n}", getattr(mod, n).weight)
     put("gqa_out", mod(xh)[0])
+
+    # --- fused RMSNorm + activation (own generator: the vectors above keep their values)
+    g2 = torch.Generator().manual_seed(2)
+    xa = (torch.randn(9, 512, generator=g2) * 3).bfloat16()
+    wa = (1 + 0.1 * torch.randn(512, generator=g2)).bfloat16()
+    put("rmsact_x", xa); put("rmsact_w", wa)
+    for act in ("mish", "quickgelu", "squared_relu"):
+        ma = FastFusedRMSNormActivation(512, eps=1e-6, activation=act, use_triton=False).bfloat16()
+        ma.weight.copy_(wa)
+        put(f"rmsact_{act}_y", ma(xa))
+        m32 = FastFusedRMSNormActivation(512, eps=1e-6, activation=act, use_triton=False)
+        m32.weight.copy_(wa.float())
+        put(f"rmsact_{act}_y_f32w", m32(xa))          # fp32 weight: product promoted to fp32
+        put(f"rmsact_{act}_y_f32", m32(xa.float()))   # fp32 activations
 
 np.savez_compressed(OUT, **vec)
 print("wrote", OUT, os.path.getsize(OUT), "bytes;", len(vec), "arrays; trinix", trinix.__version__)

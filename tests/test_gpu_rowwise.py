@@ -277,3 +277,37 @@ def test_every_op_on_exact_width_rows(cuda, nvec, rows, dtype):
         qc, qs, _ = T.ops.residual_rmsnorm_quantize(xc, rc, wc, 1e-6, return_sum=True)
         uc2, us2 = T.quantize_rowwise(yr)
         assert torch.equal(qc, uc2) and torch.equal(qs, us2)
+
+
+@pytest.mark.parametrize("act", ["mish", "quickgelu", "squared_relu"])
+def test_rmsnorm_activation_golden_and_shapes(cuda, act):
+    """activation(RMSNorm(x)) in one kernel against the reference's own vectors and the oracle:
+    bf16 weight (product rounded before the activation), fp32 weight (promoted), fp32 rows, and
+    the module above its kernel threshold."""
+    x, w = G("rmsact_x"), G("rmsact_w")
+    y = T.ops.rmsnorm_activation(x.to(cuda), w.to(cuda), 1e-6, act).cpu()
+    assert_norm_close(y, G(f"rmsact_{act}_y"))
+    y = T.ops.rmsnorm_activation(x.to(cuda), w.float().to(cuda), 1e-6, act).cpu()
+    assert_norm_close(y, G(f"rmsact_{act}_y_f32w"))
+    y = T.ops.rmsnorm_activation(x.float().to(cuda), w.float().to(cuda), 1e-6, act).cpu()
+    torch.testing.assert_close(y, G(f"rmsact_{act}_y_f32"), rtol=2e-5, atol=2e-6)
+    g = torch.Generator().manual_seed(17)
+    for rows, cols, dtype in [(40, 4096, torch.bfloat16), (3, 8192, torch.float16),
+                              (5, 1000, torch.bfloat16), (2, 4104, torch.float32),
+                              (7, 16384, torch.bfloat16)]:
+        xs = (torch.randn(rows, cols, generator=g) * 4).to(dtype)
+        ws = (1 + 0.2 * torch.randn(cols, generator=g)).to(dtype)
+        out = T.TritonFusedRMSNormActivationKernel.apply(xs.to(cuda), ws.to(cuda), 1e-6, act).cpu()
+        ref = R.rmsnorm_activation_ref(xs, ws, 1e-6, act)
+        if dtype == torch.float32:
+            assert rel_err(out, ref) <= 2e-5
+        else:
+            assert rel_err(out, ref) <= 1e-2
+    m = T.FastFusedRMSNormActivation(4096, activation=act).to(cuda).bfloat16()
+    xm = (torch.randn(2, 9, 4096, generator=g) * 2).bfloat16()
+    before = T.ops.launch_count
+    ym = m(xm.to(cuda))
+    assert T.ops.launch_count == before + 1
+    assert rel_err(ym.cpu(), R.rmsnorm_activation_ref(xm, m.weight.detach().cpu(), 1e-6, act)) <= 1e-2
+    with pytest.raises(ValueError):
+        T.ops.rmsnorm_activation(xm.to(cuda), m.weight, 1e-6, "gelu")

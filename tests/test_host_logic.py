@@ -151,6 +151,11 @@ def test_install_patches_the_reference_in_place():
             with torch.no_grad():
                 m.weight.copy_(G("rms_f32_w"))
                 torch.testing.assert_close(m(G("rms_f32_x")), G("rms_f32_y"), rtol=2e-6, atol=2e-6)
+            # the fused kernel classes live in trinix.kernels.fused and are rebound there
+            from trinix.kernels.fused import (TritonFusedResidualRMSNormKernel as RefRes,
+                                              TritonFusedRMSNormActivationKernel as RefAct)
+            assert RefRes.apply.__module__ == "trinix_b200.kernels"
+            assert RefAct.apply.__module__ == "trinix_b200.kernels"
             # the reference's own fuse() now knows the int8 pattern
             ref_fused = trinix.fuse(RefFastRMSNorm(4096), T.RowwiseInt8Quant())
             assert isinstance(ref_fused, T.FastFusedRMSNormInt8) and ref_fused.hidden_size == 4096

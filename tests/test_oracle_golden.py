@@ -36,6 +36,20 @@ def test_residual_rmsnorm():
     assert int(bf16_ulps(y, G("resrms_y")).max()) <= 1
 
 
+@pytest.mark.parametrize("act", ["mish", "quickgelu", "squared_relu"])
+def test_rmsnorm_activation(act):
+    x, w = G("rmsact_x"), G("rmsact_w")
+    y = R.rmsnorm_activation_ref(x, w, 1e-6, act)
+    assert y.dtype == torch.bfloat16
+    assert int(bf16_ulps(y, G(f"rmsact_{act}_y")).max()) <= 1
+    # fp32 weight: the product stays in fp32 before the activation, the result is bf16 again
+    y32w = R.rmsnorm_activation_ref(x, w.float(), 1e-6, act)
+    assert y32w.dtype == torch.bfloat16
+    assert int(bf16_ulps(y32w, G(f"rmsact_{act}_y_f32w")).max()) <= 1
+    y32 = R.rmsnorm_activation_ref(x.float(), w.float(), 1e-6, act)
+    torch.testing.assert_close(y32, G(f"rmsact_{act}_y_f32"), rtol=2e-6, atol=2e-6)
+
+
 def test_layernorm():
     y = R.layernorm_ref(G("ln_f32_x"), G("ln_f32_w"), G("ln_f32_b"), 1e-5)
     torch.testing.assert_close(y, G("ln_f32_y"), **F32_TOL)

@@ -12,6 +12,7 @@ from .kernels import (
     RowwiseInt8Kernel,
     TritonAttentionKernel,
     TritonFusedResidualRMSNormKernel,
+    TritonFusedRMSNormActivationKernel,
     TritonGeGLUKernel,
     TritonLayerNormKernel,
     TritonReGLUKernel,
@@ -23,6 +24,7 @@ from .layers import (
     FastALiBiPositionEmbedding,
     FastBaseAttention,
     FastFusedResidualRMSNorm,
+    FastFusedRMSNormActivation,
     FastGeGLU,
     FastGroupedQueryAttention,
     FastLayerNorm,
@@ -43,6 +45,7 @@ from .ops import (
     residual_rmsnorm,
     residual_rmsnorm_quantize,
     rmsnorm,
+    rmsnorm_activation,
     rmsnorm_quantize,
     rope,
 )

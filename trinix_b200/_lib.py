@@ -23,6 +23,8 @@ SIGNATURES = {
     "trx_status_string": (c_char_p, [c_int]),
     "trx_rmsnorm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                 c_int64, c_float, c_int, c_int, c_void_p]),
+    "trx_rmsnorm_act_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                    c_float, c_int, c_int, c_int, c_void_p]),
     "trx_layernorm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int,
                                   c_void_p]),

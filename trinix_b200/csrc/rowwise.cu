@@ -40,11 +40,12 @@ enum RowOp {
   OP_QUANT = 2,
   OP_RMSNORM_QUANT = 3,
   OP_RES_RMSNORM = 4,        // RMSNorm(x + residual)
-  OP_RES_RMSNORM_QUANT = 5   // RMSNorm(x + residual) -> int8
+  OP_RES_RMSNORM_QUANT = 5,  // RMSNorm(x + residual) -> int8
+  OP_RMSNORM_ACT = 6         // act(RMSNorm(x)), act in {mish, quickgelu, squared_relu}
 };
 __host__ __device__ constexpr bool op_is_rms(int op) {
   return op == OP_RMSNORM || op == OP_RMSNORM_QUANT || op == OP_RES_RMSNORM ||
-         op == OP_RES_RMSNORM_QUANT;
+         op == OP_RES_RMSNORM_QUANT || op == OP_RMSNORM_ACT;
 }
 __host__ __device__ constexpr bool op_has_quant(int op) {
   return op == OP_QUANT || op == OP_RMSNORM_QUANT || op == OP_RES_RMSNORM_QUANT;
@@ -86,15 +87,57 @@ struct ResParams {
   int64_t sum_stride;  // elements
 };
 struct NoRes {};
+struct ActParams {
+  int act;  // TRX_ACT_*
+};
 struct RowParams : RowParamsBase {
   ResParams rp;
+  ActParams ap;
 };
 template <int OP>
-using ResArg = std::conditional_t<op_has_res(OP), ResParams, NoRes>;
+using ResArg = std::conditional_t<op_has_res(OP), ResParams,
+                                  std::conditional_t<OP == OP_RMSNORM_ACT, ActParams, NoRes>>;
 template <int OP>
 static ResArg<OP> res_arg(const RowParams& p) {
   if constexpr (op_has_res(OP)) return p.rp;
+  else if constexpr (OP == OP_RMSNORM_ACT) return p.ap;
   else return NoRes{};
+}
+
+// Activations of the fused RMSNorm + activation op, on the fp32 value of the normalised element
+// (trinix/layers/fused/rmsnorm_activation.py:79-84). mish(n) = n * tanh(softplus(n)) with
+// tanh(ln(1 + u)) = (u^2 + 2u) / (u^2 + 2u + 2), u = e^n: one exponential and one division;
+// beyond n = 20 (torch's softplus threshold) softplus(n) = n and tanh(n) = 1 in fp32.
+// FAST (16-bit outputs): hardware exp2 on a pre-scaled argument and the approximate division,
+// both some 2^-21 relative, far below the storage rounding step; fp32 outputs take expf and the
+// IEEE division.
+template <bool FAST>
+__device__ __forceinline__ float row_exp(float x) {
+  if constexpr (FAST) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x * 1.4426950408889634f));
+    return r;
+  } else {
+    return expf(x);
+  }
+}
+template <bool FAST>
+__device__ __forceinline__ float row_div(float a, float b) {
+  if constexpr (FAST) return __fdividef(a, b);
+  else return __fdiv_rn(a, b);
+}
+template <bool FAST>
+__device__ __forceinline__ float row_act(float n, int act) {
+  if (act == TRX_ACT_MISH) {
+    // e^20 squared is already 2.4e17: q / (q + 2) == 1 in fp32 from there on, so clamping the
+    // exponent reproduces softplus's n > 20 shortcut without a branch (and keeps q finite)
+    const float u = row_exp<FAST>(fminf(n, 20.0f));
+    const float q = u * (u + 2.0f);
+    return n * row_div<FAST>(q, q + 2.0f);
+  }
+  if (act == TRX_ACT_QUICKGELU) return n * row_div<FAST>(1.0f, 1.0f + row_exp<FAST>(-1.702f * n));
+  const float r = fmaxf(n, 0.0f);  // squared ReLU
+  return r * r;
 }
 
 // Packed product of two 16-bit pairs with one rounding per lane.
@@ -354,6 +397,11 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
                 for (int j = 0; j < 4; ++j) {
                   const float2 n = mul2(f2[j], r2);
                   yu[j] = mul_packed16<T>(wu[j], P::pack2(n.x, n.y));
+                  if constexpr (OP == OP_RMSNORM_ACT) {
+                    // the activation sees the product rounded to the storage dtype
+                    const float2 a = P::cvt2(yu[j]);
+                    yu[j] = P::pack2(row_act<true>(a.x, rp.act), row_act<true>(a.y, rp.act));
+                  }
                 }
                 emit(i, col, make_uint4(yu[0], yu[1], yu[2], yu[3]));
               }
@@ -371,8 +419,12 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
               float wv[VEC];
               load_param_vec<VEC>(p.w, p.w_dtype, col, wv);
 #pragma unroll
-              for (int j = 0; j < VEC; ++j)
+              for (int j = 0; j < VEC; ++j) {
                 f[j] = __fmul_rn(wv[j], P::round(__fmul_rn(f[j], rstd)));
+                // weight of another dtype: the reference's product is promoted to fp32 and the
+                // activation sees it unrounded
+                if constexpr (OP == OP_RMSNORM_ACT) f[j] = row_act<(VEC == 8)>(f[j], rp.act);
+              }
               emit(i, col, P::pack(f));
             }
           }
@@ -488,6 +540,12 @@ __global__ void __launch_bounds__(256) row_kernel_generic(const RowParamsBase p,
         return P::round(o);
       } else if constexpr (OP == OP_QUANT) {
         return f;
+      } else if constexpr (OP == OP_RMSNORM_ACT) {
+        // same-dtype weight: the product is rounded before the activation; any other weight
+        // dtype promotes it to fp32 (trinix/layers/fused/rmsnorm_activation.py:77)
+        float n = __fmul_rn(load_param1(p.w, p.w_dtype, c), P::round(__fmul_rn(f, rstd)));
+        if (p.w_dtype == P::DTYPE) n = P::round(n);
+        return P::round(row_act<(P::VEC == 8)>(n, rp.act));
       } else {
         return P::round(
             __fmul_rn(load_param1(p.w, p.w_dtype, c), P::round(__fmul_rn(f, rstd))));
@@ -560,7 +618,8 @@ static int launch_row(const RowParams& p, cudaStream_t stream) {
   constexpr int VEC = Pack<T>::VEC;
   if (p.R == 0) return TRX_OK;
   constexpr bool HAS_QUANT = op_has_quant(OP);
-  constexpr bool WRITES_Y = (OP == OP_RMSNORM || OP == OP_LAYERNORM || OP == OP_RES_RMSNORM);
+  constexpr bool WRITES_Y = (OP == OP_RMSNORM || OP == OP_LAYERNORM || OP == OP_RES_RMSNORM ||
+                             OP == OP_RMSNORM_ACT);
   bool vec_ok = (p.C % VEC == 0) && aligned_to(p.x, 16) && (p.x_stride % VEC == 0);
   if (WRITES_Y) vec_ok = vec_ok && aligned_to(p.y, 16) && (p.y_stride % VEC == 0);
   if (HAS_QUANT) vec_ok = vec_ok && aligned_to(p.codes, VEC) && (p.codes_stride % VEC == 0);
@@ -630,6 +689,24 @@ extern "C" int trx_rmsnorm_fwd(const void* x, const void* w, void* y, float* rst
   p.R = R; p.C = C; p.x_stride = x_row_stride; p.y_stride = y_row_stride;
   p.eps = eps; p.w_dtype = w_dtype;
   return launch_row_dtype<OP_RMSNORM>(p, x_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int trx_rmsnorm_act_fwd(const void* x, const void* w, void* y, int64_t R, int64_t C,
+                                   int64_t x_row_stride, int64_t y_row_stride, float eps, int act,
+                                   int x_dtype, int w_dtype, void* stream) {
+  if (!dtype_ok(x_dtype) || !dtype_ok(w_dtype)) return TRX_ERR_DTYPE;
+  if (act != TRX_ACT_MISH && act != TRX_ACT_QUICKGELU && act != TRX_ACT_SQUARED_RELU)
+    return TRX_ERR_UNSUPPORTED;
+  if (R < 0 || C <= 0) return TRX_ERR_SHAPE;
+  if (R == 0) return TRX_OK;
+  if (!x || !w || !y) return TRX_ERR_NULL_POINTER;
+  if (x_row_stride < C || y_row_stride < C) return TRX_ERR_STRIDE;
+  RowParams p{};
+  p.x = x; p.w = w; p.y = y;
+  p.R = R; p.C = C; p.x_stride = x_row_stride; p.y_stride = y_row_stride;
+  p.eps = eps; p.w_dtype = w_dtype;
+  p.ap.act = act;
+  return launch_row_dtype<OP_RMSNORM_ACT>(p, x_dtype, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int trx_layernorm_fwd(const void* x, const void* w_or_null, const void* b_or_null,

@@ -39,8 +39,14 @@ def install(strict: bool = True):
     """
     trinix = importlib.import_module("trinix")
     kernels = importlib.import_module("trinix.kernels")
+    try:  # the fused kernel classes live one package down (trinix/kernels/fused/__init__.py)
+        fused_kernels = importlib.import_module("trinix.kernels.fused")
+    except ImportError:
+        fused_kernels = None
     for name, ours in KERNEL_CLASSES.items():
         theirs = getattr(kernels, name, None)
+        if theirs is None and fused_kernels is not None:
+            theirs = getattr(fused_kernels, name, None)
         if theirs is None:
             setattr(kernels, name, ours)
             continue

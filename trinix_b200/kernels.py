@@ -84,6 +84,19 @@ class TritonFusedResidualRMSNormKernel:
         return _run(lambda x, r, w: ops.residual_rmsnorm(x, r, w, eps), X, Residual, W)
 
 
+class TritonFusedRMSNormActivationKernel:
+    """Same interface as trinix/kernels/fused/rmsnorm_activation_kernel.py:
+    apply(X, W, eps, activation) -> activation(RMSNorm(X))."""
+
+    @staticmethod
+    def is_available() -> bool:
+        return _available()
+
+    @staticmethod
+    def apply(X: torch.Tensor, W: torch.Tensor, eps: float, activation: str = "mish") -> torch.Tensor:
+        return _run(lambda x, w: ops.rmsnorm_activation(x, w, eps, activation), X, W)
+
+
 class TritonRoPEKernel:
     """Same interface as trinix/kernels/rope_kernel.py:180-222: (q, k, cos, sin) -> (q', k')."""
 
@@ -194,6 +207,7 @@ KERNEL_CLASSES = {
     "TritonRMSNormKernel": TritonRMSNormKernel,
     "TritonLayerNormKernel": TritonLayerNormKernel,
     "TritonFusedResidualRMSNormKernel": TritonFusedResidualRMSNormKernel,
+    "TritonFusedRMSNormActivationKernel": TritonFusedRMSNormActivationKernel,
     "TritonRoPEKernel": TritonRoPEKernel,
     "TritonSwiGLUKernel": TritonSwiGLUKernel,
     "TritonGeGLUKernel": TritonGeGLUKernel,

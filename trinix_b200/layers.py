@@ -23,6 +23,7 @@ import torch.nn.functional as F
 from .functional import triton_attn_func
 from .kernels import (
     TritonFusedResidualRMSNormKernel,
+    TritonFusedRMSNormActivationKernel,
     TritonGeGLUKernel,
     TritonLayerNormKernel,
     TritonReGLUKernel,
@@ -106,6 +107,55 @@ class FastFusedResidualRMSNorm(nn.Module):
         if hidden_states.is_cuda and self._check_triton_availability():
             return self._triton_forward(hidden_states, residual)
         return self._pytorch_forward(hidden_states, residual)
+
+
+class FastFusedRMSNormActivation(nn.Module):
+    """Mirror of trinix/layers/fused/rmsnorm_activation.py:9-110: activation(RMSNorm(x)) with
+    activation in {"mish", "quickgelu", "squared_relu"} (kernel for hidden_size > 2048)."""
+
+    KERNEL_MIN_HIDDEN = 2048
+    SUPPORTED = ("mish", "quickgelu", "squared_relu")
+
+    def __init__(self, hidden_size: int, eps: float = 1e-6, activation: str = "mish",
+                 use_triton: bool = True):
+        super().__init__()
+        if activation not in self.SUPPORTED:
+            raise ValueError(f"Unsupported activation '{activation}'. "
+                             f"Supported: {sorted(self.SUPPORTED)}")
+        self.hidden_size, self.eps, self.activation = hidden_size, eps, activation
+        self.use_triton = use_triton
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+
+    def _check_triton_availability(self) -> bool:
+        return (self.use_triton and TritonFusedRMSNormActivationKernel.is_available()
+                and self.hidden_size > self.KERNEL_MIN_HIDDEN)
+
+    def _pytorch_forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        dt = hidden_states.dtype
+        h = hidden_states.to(torch.float32)
+        h = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + self.eps)
+        n = (self.weight * h.to(dt)).to(torch.float32)
+        if self.activation == "mish":
+            out = n * torch.tanh(F.softplus(n))
+        elif self.activation == "quickgelu":
+            out = n * torch.sigmoid(1.702 * n)
+        else:
+            out = torch.relu(n) ** 2
+        return out.to(dt)
+
+    def _triton_forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        flat = hidden_states.reshape(-1, self.hidden_size)
+        out = TritonFusedRMSNormActivationKernel.apply(flat, self.weight, self.eps, self.activation)
+        return out.view(hidden_states.shape)
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        if hidden_states.shape[-1] != self.hidden_size:
+            raise ValueError(
+                f"Expected hidden_states with last dimension {self.hidden_size}, "
+                f"but got shape {hidden_states.shape}")
+        if hidden_states.is_cuda and self._check_triton_availability():
+            return self._triton_forward(hidden_states)
+        return self._pytorch_forward(hidden_states)
 
 
 class FastLayerNorm(nn.Module):

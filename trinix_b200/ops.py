@@ -174,6 +174,31 @@ def rmsnorm_quantize(x: torch.Tensor, weight: torch.Tensor,
     return codes.view(x.shape), scales.view(x.shape[:-1])
 
 
+ROW_ACTIVATIONS = {"mish": 0, "quickgelu": 1, "squared_relu": 2}
+
+
+def rmsnorm_activation(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+                       activation: str = "mish") -> torch.Tensor:
+    """activation(RMSNorm(x)) in one pass; activation in {"mish", "quickgelu", "squared_relu"}."""
+    if activation not in ROW_ACTIVATIONS:
+        raise ValueError(f"Unsupported activation '{activation}'. "
+                         f"Supported: {sorted(ROW_ACTIVATIONS)}")
+    dev = _need_cuda(x, weight)
+    if weight.numel() != x.shape[-1]:
+        raise ValueError(f"weight has {weight.numel()} elements, rows have {x.shape[-1]}")
+    x2 = _rows(x)
+    w = weight.detach().contiguous()
+    y = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_rmsnorm_act_fwd(_ptr(x2), _ptr(w), _ptr(y), x2.shape[0], x2.shape[1],
+                                             _row_stride(x2), x2.shape[1], float(eps),
+                                             ROW_ACTIVATIONS[activation], _code(x2), _code(w),
+                                             _stream(dev))
+    _lib.check("trx_rmsnorm_act_fwd", rc)
+    _count()
+    return y.view(x.shape)
+
+
 def residual_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
                      eps: float = 1e-6, return_sum: bool = False):
     """RMSNorm(x + residual) with the sum kept in fp32 on chip; optionally also returns the
