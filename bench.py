@@ -207,6 +207,9 @@ def bench_ops(device, pk):
     hbm("residual_rmsnorm_quant_sum_i8_32768x4096", R_ * C_ * 7 + 4 * R_ + 2 * C_,
         [lambda a=a, r=r: ops.residual_rmsnorm_quantize(a, r, w, 1e-6, True)
          for a, r in ((acts[0], acts[1]), (acts[1], acts[0]))])
+    hbm("residual_layernorm_sum_bf16_32768x4096", R_ * C_ * 8 + 4 * C_,
+        [lambda a=a, r=r: ops.residual_layernorm(a, r, w, b, 1e-5, True)
+         for a, r in ((acts[0], acts[1]), (acts[1], acts[0]))])
     for act in ("mish", "quickgelu", "squared_relu"):
         hbm(f"rmsnorm_{act}_bf16_32768x4096", R_ * C_ * 4 + 2 * C_,
             [lambda a=a, act=act: ops.rmsnorm_activation(a, w, 1e-6, act) for a in acts])

@@ -143,6 +143,24 @@ int trx_residual_rmsnorm_fwd(const void* x, const void* residual, const void* w,
                              void* stream);
 
 /*
+ * Fused residual add + LayerNorm: s = float(x) + float(residual) (fp32, on chip),
+ *   y = round(round(w * round((s - mean(s)) * rstd)) + b)  — the normalised value is cast to the
+ *   activation dtype before the affine part, which runs in the parameters' dtype (a parameter
+ *   dtype other than the activation's promotes to fp32 and rounds once at the end);
+ *   sum_out_or_null receives round(s). w and b may be NULL.
+ * Follows FastFusedResidualLayerNorm._pytorch_forward,
+ * trinix/layers/fused/residual_layernorm.py:66-73; replaces
+ * TritonFusedResidualLayerNormKernel.apply, trinix/kernels/fused/residual_layernorm_kernel.py
+ * (kernel :9-79).
+ */
+int trx_residual_layernorm_fwd(const void* x, const void* residual, const void* w_or_null,
+                               const void* b_or_null, void* y, void* sum_out_or_null,
+                               float* mean_or_null, float* rstd_or_null, int64_t R, int64_t C,
+                               int64_t x_row_stride, int64_t res_row_stride, int64_t y_row_stride,
+                               int64_t sum_row_stride, float eps, int x_dtype, int w_dtype,
+                               void* stream);
+
+/*
  * Fused residual add + RMSNorm -> int8: quantises exactly the rows trx_residual_rmsnorm_fwd
  * would write, without writing them; optionally writes the summed residual stream.
  * No counterpart in the reference (it has no int8 code).

@@ -26,6 +26,7 @@ from trinix.layers.embeddings.alibi import FastALiBiPositionEmbedding  # noqa: E
 from trinix.layers.embeddings.rope import FastRoPEPositionEmbedding  # noqa: E402
 from trinix.layers.norm.layernorm import FastLayerNorm  # noqa: E402
 from trinix.layers.norm.rmsnorm import FastRMSNorm  # noqa: E402
+from trinix.layers.fused.residual_layernorm import FastFusedResidualLayerNorm  # noqa: E402
 from trinix.layers.fused.residual_rmsnorm import FastFusedResidualRMSNorm  # noqa: E402
 from trinix.layers.fused.rmsnorm_activation import FastFusedRMSNormActivation  # noqa: E402
 
@@ -145,6 +146,21 @@ with torch.no_grad():
         m32.weight.copy_(wa.float())
         put(f"rmsact_{act}_y_f32w", m32(xa))          # fp32 weight: product promoted to fp32
         put(f"rmsact_{act}_y_f32", m32(xa.float()))   # fp32 activations
+
+    # --- fused residual + LayerNorm (own generator), bf16 / fp32 parameters / fp32 activations
+    g3 = torch.Generator().manual_seed(3)
+    xl2 = (torch.randn(11, 384, generator=g3) * 2 + 0.5).bfloat16()
+    rl2 = torch.randn(11, 384, generator=g3).bfloat16()
+    wl2 = (1 + 0.1 * torch.randn(384, generator=g3)).bfloat16()
+    bl2 = (0.1 * torch.randn(384, generator=g3)).bfloat16()
+    put("resln_x", xl2); put("resln_r", rl2); put("resln_w", wl2); put("resln_b", bl2)
+    mlr = FastFusedResidualLayerNorm(384, eps=1e-5, use_triton=False).bfloat16()
+    mlr.weight.copy_(wl2); mlr.bias.copy_(bl2)
+    put("resln_y", mlr(xl2, rl2))
+    mlr32 = FastFusedResidualLayerNorm(384, eps=1e-5, use_triton=False)
+    mlr32.weight.copy_(wl2.float()); mlr32.bias.copy_(bl2.float())
+    put("resln_y_f32w", mlr32(xl2, rl2))                   # fp32 parameters: promoted to fp32
+    put("resln_y_f32", mlr32(xl2.float(), rl2.float()))    # fp32 activations
 
 np.savez_compressed(OUT, **vec)
 print("wrote", OUT, os.path.getsize(OUT), "bytes;", len(vec), "arrays; trinix", trinix.__version__)

@@ -122,6 +122,8 @@ def test_empty_inputs_every_op(cuda):
     assert c.shape == (0, 4096) and s.shape == (0,)
     y, h = T.ops.residual_rmsnorm(x0, x0, w, 1e-6, return_sum=True)
     assert y.shape == (0, 4096) and h.shape == (0, 4096)
+    y, h = T.ops.residual_layernorm(x0, x0, w, w, 1e-5, return_sum=True)
+    assert y.shape == (0, 4096) and h.shape == (0, 4096)
     assert T.ops.glu(torch.empty(0, 2 * 512, device=cuda, dtype=torch.bfloat16), "swiglu").shape == (0, 512)
     q0 = torch.empty(0, 16, 4, 128, device=cuda, dtype=torch.bfloat16)
     cos = torch.ones(16, 128, device=cuda)

@@ -230,6 +230,84 @@ def test_residual_rmsnorm_golden_and_shapes(cuda):
             assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 2e-3
 
 
+def _assert_resln_close(y, x, r, w, b, eps=1e-5):
+    """LayerNorm(x + r) against the oracle. fp32: 1e-5 relative. 16-bit: the kernel follows the
+    oracle's rounding order round(round(w * round(n)) + b); the statistics can differ in their
+    last fp32 bits (summation order), which now and then flips the inner rounding by one ulp. So:
+    any difference in fewer than 0.2 % of the elements, beyond 1e-2 relative in at most 1e-5 of
+    them, and never further than four rounding steps of the larger of the two terms of the final
+    sum (plus 1e-5 absolute: where x + r sits on the row mean, the normalised value is only as
+    good as the last bits of that mean)."""
+    ref = R.residual_layernorm_ref(x, r, w, b, eps)
+    if x.dtype == torch.float32:
+        assert y.dtype == torch.float32 and rel_err(y, ref) <= 1e-5
+        return
+    ref = ref.to(x.dtype)  # fp32 parameters promote the oracle's result; the kernel rounds once
+    assert y.dtype == ref.dtype and y.shape == ref.shape
+    assert float((y != ref).float().mean()) < 2e-3
+    err = (y.double() - ref.double()).abs()
+    floor = 1e-2 * float(ref.double().pow(2).mean().sqrt())
+    assert float((err > 1e-2 * ref.double().abs().clamp_min(floor)).float().mean()) <= 1e-5
+    n = R.residual_layernorm_ref(x, r, None, None, eps).double()
+    terms = (n * (w.double() if w is not None else 1.0)).abs()
+    if b is not None:
+        terms = torch.maximum(terms, b.double().abs().expand_as(terms))
+    step = 2.0 ** (-7 if x.dtype == torch.bfloat16 else -10)
+    assert bool((err <= 4 * step * terms + 1e-5).all()), float((err - 4 * step * terms).max())
+
+
+def test_residual_layernorm_golden_and_shapes(cuda):
+    """LayerNorm(x + residual) in one kernel against the reference's own vectors and the oracle:
+    16-bit parameters (affine part rounded step by step), fp32 parameters (promoted), fp32 rows,
+    missing weight / bias, rows on the vector and on the scalar path, the summed stream, and the
+    mirror module above its kernel threshold."""
+    x, r, w, b = G("resln_x"), G("resln_r"), G("resln_w"), G("resln_b")
+    xc, rc = x.to(cuda), r.to(cuda)
+    y = T.TritonFusedResidualLayerNormKernel.apply(xc, rc, w.to(cuda), b.to(cuda), 1e-5).cpu()
+    assert int(bf16_ulps(y, G("resln_y")).max()) <= 1
+    assert float((y != G("resln_y")).float().mean()) < 2e-3
+    y = T.ops.residual_layernorm(xc, rc, w.float().to(cuda), b.float().to(cuda), 1e-5).cpu()
+    assert int(bf16_ulps(y, G("resln_y_f32w").bfloat16()).max()) <= 1
+    y = T.ops.residual_layernorm(xc.float(), rc.float(), w.float().to(cuda), b.float().to(cuda),
+                                 1e-5).cpu()
+    torch.testing.assert_close(y, G("resln_y_f32"), rtol=2e-5, atol=2e-6)
+    g = torch.Generator().manual_seed(23)
+    for rows, cols, dtype in [(64, 4096, torch.bfloat16), (5, 8192, torch.bfloat16),
+                              (3, 777, torch.bfloat16), (4, 4104, torch.float32),
+                              (2, 40000, torch.float16), (3, 520, torch.float16),
+                              (304, 2048, torch.bfloat16), (9, 32768, torch.bfloat16),
+                              (2, 65536, torch.float32)]:
+        xs = (torch.randn(rows, cols, generator=g) + 0.3).to(dtype)
+        rs = (torch.randn(rows, cols, generator=g) * 3).to(dtype)
+        ws = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype)
+        bs = (0.1 * torch.randn(cols, generator=g)).to(dtype)
+        xd, rd, wd, bd = xs.to(cuda), rs.to(cuda), ws.to(cuda), bs.to(cuda)
+        y, s = T.ops.residual_layernorm(xd, rd, wd, bd, 1e-5, return_sum=True)
+        _assert_resln_close(y.cpu(), xs, rs, ws, bs)
+        assert torch.equal(s.cpu(), (xs.float() + rs.float()).to(dtype))
+        _assert_resln_close(T.ops.residual_layernorm(xd, rd, None, None, 1e-5).cpu(),
+                            xs, rs, None, None)
+        _assert_resln_close(T.ops.residual_layernorm(xd, rd, wd, None, 1e-5).cpu(),
+                            xs, rs, ws, None)
+        if dtype != torch.float32:
+            _assert_resln_close(T.ops.residual_layernorm(xd, rd, wd.float(), bd.float(), 1e-5).cpu(),
+                                xs, rs, ws.float(), bs.float())
+    # rows given as a strided view (row stride > C), through the mirror module
+    big = torch.randn(6, 2 * 4104, generator=g).bfloat16()
+    res = torch.randn(6, 4104, generator=g).bfloat16()
+    m = T.FastFusedResidualLayerNorm(4104).bfloat16().to(cuda)
+    with torch.no_grad():
+        m.weight.copy_((1 + 0.1 * torch.randn(4104, generator=g)).bfloat16())
+        m.bias.copy_((0.1 * torch.randn(4104, generator=g)).bfloat16())
+        assert m._check_triton_availability()
+        view = big.to(cuda)[:, :4104]
+        y = m(view, res.to(cuda))
+        _assert_resln_close(y.cpu(), big[:, :4104], res, m.weight.detach().cpu(),
+                            m.bias.detach().cpu())
+    with pytest.raises(ValueError):
+        T.ops.residual_layernorm(xc, rc[:, :8], None, None)
+
+
 def test_residual_rmsnorm_quant_equals_unfused_bit_exact(cuda):
     g = torch.Generator().manual_seed(12)
     for rows, cols, dtype in [(512, 4096, torch.bfloat16), (7, 1000, torch.bfloat16),

@@ -10,7 +10,7 @@ import torch
 import trinix_b200 as T
 from oracle import reference_port as R
 from trinix_b200 import sharding
-from tests.util import Golden
+from tests.util import Golden, bf16_ulps
 
 G = Golden()
 REFERENCE_DIR = os.environ.get("TRINIX_REFERENCE", "/root/reference")
@@ -50,6 +50,9 @@ def test_mirror_modules_take_torch_path_on_cpu_and_match_oracle():
         fr = T.FastFusedResidualRMSNorm(512, eps=1e-6).bfloat16()
         fr.weight.copy_(G("resrms_w"))
         assert torch.equal(fr(G("resrms_x"), G("resrms_r")), G("resrms_y"))
+        fl = T.FastFusedResidualLayerNorm(384, eps=1e-5).bfloat16()
+        fl.weight.copy_(G("resln_w")); fl.bias.copy_(G("resln_b"))
+        assert int(bf16_ulps(fl(G("resln_x"), G("resln_r")), G("resln_y")).max()) <= 1
         for name, cls in (("swiglu", T.FastSwiGLU), ("geglu", T.FastGeGLU), ("reglu", T.FastReGLU)):
             torch.testing.assert_close(cls(96)(G(f"{name}_f32_x")), G(f"{name}_f32_y"),
                                        rtol=2e-6, atol=2e-6)
@@ -152,9 +155,11 @@ def test_install_patches_the_reference_in_place():
                 m.weight.copy_(G("rms_f32_w"))
                 torch.testing.assert_close(m(G("rms_f32_x")), G("rms_f32_y"), rtol=2e-6, atol=2e-6)
             # the fused kernel classes live in trinix.kernels.fused and are rebound there
-            from trinix.kernels.fused import (TritonFusedResidualRMSNormKernel as RefRes,
+            from trinix.kernels.fused import (TritonFusedResidualLayerNormKernel as RefResLN,
+                                              TritonFusedResidualRMSNormKernel as RefRes,
                                               TritonFusedRMSNormActivationKernel as RefAct)
             assert RefRes.apply.__module__ == "trinix_b200.kernels"
+            assert RefResLN.apply.__module__ == "trinix_b200.kernels"
             assert RefAct.apply.__module__ == "trinix_b200.kernels"
             # the reference's own fuse() now knows the int8 pattern
             ref_fused = trinix.fuse(RefFastRMSNorm(4096), T.RowwiseInt8Quant())

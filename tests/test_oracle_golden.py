@@ -36,6 +36,18 @@ def test_residual_rmsnorm():
     assert int(bf16_ulps(y, G("resrms_y")).max()) <= 1
 
 
+def test_residual_layernorm():
+    x, r, w, b = G("resln_x"), G("resln_r"), G("resln_w"), G("resln_b")
+    y = R.residual_layernorm_ref(x, r, w, b, 1e-5)
+    assert y.dtype == torch.bfloat16
+    assert int(bf16_ulps(y, G("resln_y")).max()) <= 1
+    y32w = R.residual_layernorm_ref(x, r, w.float(), b.float(), 1e-5)
+    assert y32w.dtype == torch.float32  # reference behaviour: fp32 parameters promote
+    torch.testing.assert_close(y32w, G("resln_y_f32w"), **F32_TOL)
+    y32 = R.residual_layernorm_ref(x.float(), r.float(), w.float(), b.float(), 1e-5)
+    torch.testing.assert_close(y32, G("resln_y_f32"), **F32_TOL)
+
+
 @pytest.mark.parametrize("act", ["mish", "quickgelu", "squared_relu"])
 def test_rmsnorm_activation(act):
     x, w = G("rmsact_x"), G("rmsact_w")

@@ -11,6 +11,7 @@ from .install import install, uninstall
 from .kernels import (
     RowwiseInt8Kernel,
     TritonAttentionKernel,
+    TritonFusedResidualLayerNormKernel,
     TritonFusedResidualRMSNormKernel,
     TritonFusedRMSNormActivationKernel,
     TritonGeGLUKernel,
@@ -23,6 +24,7 @@ from .kernels import (
 from .layers import (
     FastALiBiPositionEmbedding,
     FastBaseAttention,
+    FastFusedResidualLayerNorm,
     FastFusedResidualRMSNorm,
     FastFusedRMSNormActivation,
     FastGeGLU,
@@ -42,6 +44,7 @@ from .ops import (
     glu_pair,
     layernorm,
     quantize_rowwise,
+    residual_layernorm,
     residual_rmsnorm,
     residual_rmsnorm_quantize,
     rmsnorm,

@@ -37,6 +37,9 @@ SIGNATURES = {
     "trx_residual_rmsnorm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                          c_float, c_int, c_int, c_void_p]),
+    "trx_residual_layernorm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                           c_int64, c_int64, c_float, c_int, c_int, c_void_p]),
     "trx_residual_rmsnorm_quant_i8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_int64, c_int64, c_int64, c_int64,
                                               c_int64, c_int64, c_float, c_int, c_int, c_void_p]),

@@ -1,7 +1,7 @@
-// Row kernels: RMSNorm, LayerNorm, per-row int8 quantise, fused RMSNorm -> int8, and the
-// residual forms RMSNorm(x + r) and RMSNorm(x + r) -> int8.
+// Row kernels: RMSNorm, LayerNorm, per-row int8 quantise, fused RMSNorm -> int8, the residual
+// forms RMSNorm(x + r), RMSNorm(x + r) -> int8 and LayerNorm(x + r), and act(RMSNorm(x)).
 //
-// One skeleton serves the six ops. A row is read from HBM exactly once with
+// One skeleton serves the eight ops. A row is read from HBM exactly once with
 // 128-bit streaming loads and then lives in registers (VPT 16-byte vectors per
 // thread, TPR threads per row); statistics are reduced with warp shuffles
 // (plus one shared-memory hop when a row spans more than one warp), and the
@@ -41,8 +41,10 @@ enum RowOp {
   OP_RMSNORM_QUANT = 3,
   OP_RES_RMSNORM = 4,        // RMSNorm(x + residual)
   OP_RES_RMSNORM_QUANT = 5,  // RMSNorm(x + residual) -> int8
-  OP_RMSNORM_ACT = 6         // act(RMSNorm(x)), act in {mish, quickgelu, squared_relu}
+  OP_RMSNORM_ACT = 6,        // act(RMSNorm(x)), act in {mish, quickgelu, squared_relu}
+  OP_RES_LAYERNORM = 7       // LayerNorm(x + residual)
 };
+__host__ __device__ constexpr bool op_is_ln(int op) { return op == OP_LAYERNORM || op == OP_RES_LAYERNORM; }
 __host__ __device__ constexpr bool op_is_rms(int op) {
   return op == OP_RMSNORM || op == OP_RMSNORM_QUANT || op == OP_RES_RMSNORM ||
          op == OP_RES_RMSNORM_QUANT || op == OP_RMSNORM_ACT;
@@ -50,7 +52,9 @@ __host__ __device__ constexpr bool op_is_rms(int op) {
 __host__ __device__ constexpr bool op_has_quant(int op) {
   return op == OP_QUANT || op == OP_RMSNORM_QUANT || op == OP_RES_RMSNORM_QUANT;
 }
-__host__ __device__ constexpr bool op_has_res(int op) { return op == OP_RES_RMSNORM || op == OP_RES_RMSNORM_QUANT; }
+__host__ __device__ constexpr bool op_has_res(int op) {
+  return op == OP_RES_RMSNORM || op == OP_RES_RMSNORM_QUANT || op == OP_RES_LAYERNORM;
+}
 // Minimum resident CTAs per SM asked of the compiler (caps registers per thread): a thread
 // budget per SM that was measured per family, divided by the CTA size.
 __host__ __device__ constexpr int row_min_blocks(int op, int tpr, int vpt) {
@@ -179,7 +183,7 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
   constexpr int VEC = P::VEC;
   constexpr int BLOCK = TPR > 32 ? TPR : 256;
   constexpr int ROWS_PER_CTA = BLOCK / TPR;
-  constexpr bool HAS_NORM = op_is_rms(OP) || OP == OP_LAYERNORM;
+  constexpr bool HAS_NORM = op_is_rms(OP) || op_is_ln(OP);
   constexpr bool HAS_QUANT = op_has_quant(OP);
   constexpr bool HAS_RES = op_has_res(OP);
   constexpr bool NORM_TO_REGS = (OP == OP_RMSNORM_QUANT || OP == OP_RES_RMSNORM_QUANT);
@@ -217,7 +221,7 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
     }
     // Measured per op: it pays where a row costs two HBM streams (residual forms, +10-16 %) or
     // two passes over the registers (LayerNorm, +4 %), and costs 5-8 % on the others.
-        if constexpr (TRX_ROW_L2_PREFETCH > 0 && (HAS_RES || OP == OP_LAYERNORM)) {
+        if constexpr (TRX_ROW_L2_PREFETCH > 0 && (HAS_RES || op_is_ln(OP))) {
       // While this row is in flight, have the row this CTA takes next pulled from HBM into L2, so
       // that its loads find it there: the only rows a CTA waits for at HBM latency are its first.
       const int64_t prow = row + TRX_ROW_L2_PREFETCH * row_step;
@@ -232,37 +236,41 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
     (void)xf;
 
     float mean = 0.0f, rstd = 1.0f;
+    // Residual forms: f2 (vector i of x, unpacked) += the residual's vector; the sum is formed and
+    // normalised in fp32, as the reference's PyTorch paths do (layers/fused/residual_rmsnorm.py:
+    // 66-73, residual_layernorm.py:66-73), and optionally written out rounded. The host
+    // guarantees a configuration that keeps the fp32 sum on chip.
+    auto add_residual = [&](int i, float2 (&f2)[VEC / 2]) {
+      if constexpr (HAS_RES) {
+        const T* rrow = reinterpret_cast<const T*>(rp.res) + (FULL || row_ok ? row : 0) * rp.res_stride;
+        T* srow = reinterpret_cast<T*>(rp.sum_out) + (FULL || row_ok ? row : 0) * rp.sum_stride;
+        const int v = i * TPR + t;
+        if (live(i)) {
+          const int64_t col = static_cast<int64_t>(v) * VEC;
+          float2 r2[VEC / 2];
+          P::unpack2(ld_stream16(rrow + col), r2);
+#pragma unroll
+          for (int j = 0; j < VEC / 2; ++j) f2[j] = add2(f2[j], r2[j]);
+          if constexpr (VEC == 4) {
+            raw[i] = make_uint4(__float_as_uint(f2[0].x), __float_as_uint(f2[0].y),
+                                __float_as_uint(f2[1].x), __float_as_uint(f2[1].y));
+            if (rp.sum_out) st_stream16(srow + col, raw[i]);
+          } else {
+            if (rp.sum_out)
+              st_stream16(srow + col, make_uint4(P::pack2(f2[0].x, f2[0].y), P::pack2(f2[1].x, f2[1].y),
+                                                 P::pack2(f2[2].x, f2[2].y), P::pack2(f2[3].x, f2[3].y)));
+          }
+        }
+      }
+    };
     // ---- 2. statistics -------------------------------------------------------------
     if constexpr (op_is_rms(OP)) {
       float2 ss2 = make_float2(0.0f, 0.0f), ss2b = make_float2(0.0f, 0.0f);  // two chains
-      // residual variants: the host guarantees a configuration that keeps fp32 copies
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         float2 f2[VEC / 2];
         P::unpack2(raw[i], f2);
-        if constexpr (HAS_RES) {
-          const T* rrow = reinterpret_cast<const T*>(rp.res) + (FULL || row_ok ? row : 0) * rp.res_stride;
-          T* srow = reinterpret_cast<T*>(rp.sum_out) + (FULL || row_ok ? row : 0) * rp.sum_stride;
-          // residual stream: the sum is formed and normalised in fp32, as the reference's
-          // PyTorch path does (layers/fused/residual_rmsnorm.py:66-73)
-          const int v = i * TPR + t;
-          if (live(i)) {
-            const int64_t col = static_cast<int64_t>(v) * VEC;
-            float2 r2[VEC / 2];
-            P::unpack2(ld_stream16(rrow + col), r2);
-#pragma unroll
-            for (int j = 0; j < VEC / 2; ++j) f2[j] = add2(f2[j], r2[j]);
-            if constexpr (VEC == 4) {
-              raw[i] = make_uint4(__float_as_uint(f2[0].x), __float_as_uint(f2[0].y),
-                                  __float_as_uint(f2[1].x), __float_as_uint(f2[1].y));
-              if (rp.sum_out) st_stream16(srow + col, raw[i]);
-            } else {
-              if (rp.sum_out)
-                st_stream16(srow + col, make_uint4(P::pack2(f2[0].x, f2[0].y), P::pack2(f2[1].x, f2[1].y),
-                                                   P::pack2(f2[2].x, f2[2].y), P::pack2(f2[3].x, f2[3].y)));
-            }
-          }
-        }
+        add_residual(i, f2);
 #pragma unroll
         for (int j = 0; j < VEC / 2; ++j) {
           if (j & 1) ss2b = fma2(f2[j], f2[j], ss2b);
@@ -280,12 +288,13 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
       }
       float ss = row_reduce<TPR, false>(ss2.x + ss2.y, red, sel);
       rstd = rsqrt_approx(fmaf(ss, inv_C, p.eps));
-    } else if constexpr (OP == OP_LAYERNORM) {
+    } else if constexpr (op_is_ln(OP)) {
       float2 s2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         float2 f2[VEC / 2];
         P::unpack2(raw[i], f2);
+        add_residual(i, f2);
 #pragma unroll
         for (int j = 0; j < VEC / 2; ++j) {
           s2 = add2(s2, f2[j]);
@@ -321,7 +330,7 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
     if constexpr (HAS_NORM) {
       if (row_ok && t == 0) {
         if (p.rstd) p.rstd[row] = rstd;
-        if (OP == OP_LAYERNORM && p.mean) p.mean[row] = mean;
+        if (op_is_ln(OP) && p.mean) p.mean[row] = mean;
       }
     }
 
@@ -338,7 +347,7 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
           st_stream16(yrow + col, packed);
         }
       };
-      if constexpr (OP == OP_LAYERNORM) {
+      if constexpr (op_is_ln(OP)) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
           const int v = i * TPR + t;
@@ -360,8 +369,20 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
 #pragma unroll
             for (int j = 0; j < VEC; ++j) {
               float o = (f[j] - mean) * rstd;
-              if (p.w) o *= wv[j];
-              if (p.b) o += bv[j];
+              if constexpr (OP == OP_RES_LAYERNORM) {
+                // the reference's fused module casts the normalised value to the input dtype
+                // before the affine part and runs that in the parameters' dtype
+                // (residual_layernorm.py:73); plain LayerNorm (F.layer_norm) rounds once
+                o = P::round(o);
+                if (p.w) {
+                  o *= wv[j];
+                  if (p.w_dtype == P::DTYPE) o = P::round(o);
+                }
+                if (p.b) o += bv[j];
+              } else {
+                if (p.w) o *= wv[j];
+                if (p.b) o += bv[j];
+              }
               f[j] = o;
             }
             emit(i, col, P::pack(f));
@@ -514,14 +535,18 @@ __global__ void __launch_bounds__(256) row_kernel_generic(const RowParamsBase p,
       }
       ss = row_reduce<256, false>(ss, red, sel);
       rstd = rsqrt_approx(fmaf(ss, inv_C, p.eps));
-    } else if constexpr (OP == OP_LAYERNORM) {
+    } else if constexpr (op_is_ln(OP)) {
       float s = 0.0f;
-      for (int64_t c = threadIdx.x; c < p.C; c += 256) s += P::load1(xrow + c);
+      for (int64_t c = threadIdx.x; c < p.C; c += 256) {
+        const float f = xval(c);
+        s += f;
+        if (srow) P::store1(srow + c, f);
+      }
       s = row_reduce<256, false>(s, red, sel);
       mean = s * inv_C;
       float cs = 0.0f;
       for (int64_t c = threadIdx.x; c < p.C; c += 256) {
-        const float d = P::load1(xrow + c) - mean;
+        const float d = xval(c) - mean;
         cs = fmaf(d, d, cs);
       }
       cs = row_reduce<256, false>(cs, red, sel);
@@ -529,13 +554,21 @@ __global__ void __launch_bounds__(256) row_kernel_generic(const RowParamsBase p,
     }
     if (OP != OP_QUANT && threadIdx.x == 0) {
       if (p.rstd) p.rstd[row] = rstd;
-      if (OP == OP_LAYERNORM && p.mean) p.mean[row] = mean;
+      if (op_is_ln(OP) && p.mean) p.mean[row] = mean;
     }
     auto normed = [&](int64_t c) -> float {
       const float f = xval(c);
       if constexpr (OP == OP_LAYERNORM) {
         float o = (f - mean) * rstd;
         if (p.w) o *= load_param1(p.w, p.w_dtype, c);
+        if (p.b) o += load_param1(p.b, p.w_dtype, c);
+        return P::round(o);
+      } else if constexpr (OP == OP_RES_LAYERNORM) {
+        float o = P::round((f - mean) * rstd);  // rounding order of residual_layernorm.py:73
+        if (p.w) {
+          o *= load_param1(p.w, p.w_dtype, c);
+          if (p.w_dtype == P::DTYPE) o = P::round(o);
+        }
         if (p.b) o += load_param1(p.b, p.w_dtype, c);
         return P::round(o);
       } else if constexpr (OP == OP_QUANT) {
@@ -619,7 +652,7 @@ static int launch_row(const RowParams& p, cudaStream_t stream) {
   if (p.R == 0) return TRX_OK;
   constexpr bool HAS_QUANT = op_has_quant(OP);
   constexpr bool WRITES_Y = (OP == OP_RMSNORM || OP == OP_LAYERNORM || OP == OP_RES_RMSNORM ||
-                             OP == OP_RMSNORM_ACT);
+                             OP == OP_RMSNORM_ACT || OP == OP_RES_LAYERNORM);
   bool vec_ok = (p.C % VEC == 0) && aligned_to(p.x, 16) && (p.x_stride % VEC == 0);
   if (WRITES_Y) vec_ok = vec_ok && aligned_to(p.y, 16) && (p.y_stride % VEC == 0);
   if (HAS_QUANT) vec_ok = vec_ok && aligned_to(p.codes, VEC) && (p.codes_stride % VEC == 0);
@@ -774,6 +807,29 @@ extern "C" int trx_residual_rmsnorm_fwd(const void* x, const void* residual, con
   p.y_stride = y_row_stride; p.rp.sum_stride = sum_row_stride;
   p.eps = eps; p.w_dtype = w_dtype;
   return launch_row_dtype<OP_RES_RMSNORM>(p, x_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int trx_residual_layernorm_fwd(const void* x, const void* residual,
+                                          const void* w_or_null, const void* b_or_null, void* y,
+                                          void* sum_out_or_null, float* mean_or_null,
+                                          float* rstd_or_null, int64_t R, int64_t C,
+                                          int64_t x_row_stride, int64_t res_row_stride,
+                                          int64_t y_row_stride, int64_t sum_row_stride, float eps,
+                                          int x_dtype, int w_dtype, void* stream) {
+  if (!dtype_ok(x_dtype) || !dtype_ok(w_dtype)) return TRX_ERR_DTYPE;
+  if (R < 0 || C <= 0) return TRX_ERR_SHAPE;
+  if (R == 0) return TRX_OK;
+  if (!x || !residual || !y) return TRX_ERR_NULL_POINTER;
+  if (x_row_stride < C || res_row_stride < C || y_row_stride < C ||
+      (sum_out_or_null && sum_row_stride < C))
+    return TRX_ERR_STRIDE;
+  RowParams p{};
+  p.x = x; p.rp.res = residual; p.rp.sum_out = sum_out_or_null; p.w = w_or_null; p.b = b_or_null;
+  p.y = y; p.mean = mean_or_null; p.rstd = rstd_or_null;
+  p.R = R; p.C = C; p.x_stride = x_row_stride; p.rp.res_stride = res_row_stride;
+  p.y_stride = y_row_stride; p.rp.sum_stride = sum_row_stride;
+  p.eps = eps; p.w_dtype = w_dtype;
+  return launch_row_dtype<OP_RES_LAYERNORM>(p, x_dtype, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int trx_residual_rmsnorm_quant_i8(const void* x, const void* residual, const void* w,

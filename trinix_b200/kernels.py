@@ -84,6 +84,20 @@ class TritonFusedResidualRMSNormKernel:
         return _run(lambda x, r, w: ops.residual_rmsnorm(x, r, w, eps), X, Residual, W)
 
 
+class TritonFusedResidualLayerNormKernel:
+    """Same interface as trinix/kernels/fused/residual_layernorm_kernel.py:338-380:
+    apply(X, Residual, W, b, eps) -> LayerNorm(X + Residual); W and b may be None."""
+
+    @staticmethod
+    def is_available() -> bool:
+        return _available()
+
+    @staticmethod
+    def apply(X: torch.Tensor, Residual: torch.Tensor, W: Optional[torch.Tensor],
+              b: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+        return _run(lambda x, r, w, bb: ops.residual_layernorm(x, r, w, bb, eps), X, Residual, W, b)
+
+
 class TritonFusedRMSNormActivationKernel:
     """Same interface as trinix/kernels/fused/rmsnorm_activation_kernel.py:
     apply(X, W, eps, activation) -> activation(RMSNorm(X))."""
@@ -207,6 +221,7 @@ KERNEL_CLASSES = {
     "TritonRMSNormKernel": TritonRMSNormKernel,
     "TritonLayerNormKernel": TritonLayerNormKernel,
     "TritonFusedResidualRMSNormKernel": TritonFusedResidualRMSNormKernel,
+    "TritonFusedResidualLayerNormKernel": TritonFusedResidualLayerNormKernel,
     "TritonFusedRMSNormActivationKernel": TritonFusedRMSNormActivationKernel,
     "TritonRoPEKernel": TritonRoPEKernel,
     "TritonSwiGLUKernel": TritonSwiGLUKernel,

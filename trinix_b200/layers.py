@@ -22,6 +22,7 @@ import torch.nn.functional as F
 
 from .functional import triton_attn_func
 from .kernels import (
+    TritonFusedResidualLayerNormKernel,
     TritonFusedResidualRMSNormKernel,
     TritonFusedRMSNormActivationKernel,
     TritonGeGLUKernel,
@@ -107,6 +108,51 @@ class FastFusedResidualRMSNorm(nn.Module):
         if hidden_states.is_cuda and self._check_triton_availability():
             return self._triton_forward(hidden_states, residual)
         return self._pytorch_forward(hidden_states, residual)
+
+
+class FastFusedResidualLayerNorm(nn.Module):
+    """Mirror of trinix/layers/fused/residual_layernorm.py:7-93: LayerNorm(hidden_states +
+    residual) with the sum and the statistics in fp32 and the affine part applied to the value
+    rounded to the input dtype (kernel for hidden_size > 4096)."""
+
+    KERNEL_MIN_HIDDEN = 4096
+
+    def __init__(self, hidden_size: int, eps: float = 1e-5, use_triton: bool = True):
+        super().__init__()
+        self.hidden_size, self.eps, self.use_triton = hidden_size, eps, use_triton
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+        self.bias = nn.Parameter(torch.zeros(hidden_size))
+
+    def _check_triton_availability(self) -> bool:
+        return (self.use_triton and TritonFusedResidualLayerNormKernel.is_available()
+                and self.hidden_size > self.KERNEL_MIN_HIDDEN)
+
+    def _pytorch_forward(self, hidden_states: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        dt = hidden_states.dtype
+        s = hidden_states.to(torch.float32) + residual.to(torch.float32)
+        mean = s.mean(-1, keepdim=True)
+        var = (s - mean).pow(2).mean(-1, keepdim=True)
+        s = (s - mean) * torch.rsqrt(var + self.eps)
+        return (self.weight * s.to(dt)) + self.bias
+
+    def _triton_forward(self, hidden_states: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        flat = hidden_states.reshape(-1, self.hidden_size)
+        res = residual.reshape(-1, self.hidden_size)
+        out = TritonFusedResidualLayerNormKernel.apply(flat, res, self.weight, self.bias, self.eps)
+        return out.view(hidden_states.shape)
+
+    def forward(self, hidden_states: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        if hidden_states.shape[-1] != self.hidden_size:
+            raise ValueError(
+                f"Expected hidden_states with last dimension {self.hidden_size}, "
+                f"but got shape {hidden_states.shape}")
+        if hidden_states.is_cuda and self._check_triton_availability():
+            return self._triton_forward(hidden_states, residual)
+        return self._pytorch_forward(hidden_states, residual)
+
+    def extra_repr(self) -> str:
+        backend = "triton" if self._check_triton_availability() else "pytorch"
+        return f"hidden_size={self.hidden_size}, eps={self.eps}, backend={backend}"
 
 
 class FastFusedRMSNormActivation(nn.Module):

@@ -223,6 +223,35 @@ def residual_rmsnorm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tens
     return (y, s.view(x.shape)) if return_sum else y
 
 
+def residual_layernorm(x: torch.Tensor, residual: torch.Tensor, weight: Optional[torch.Tensor],
+                       bias: Optional[torch.Tensor], eps: float = 1e-5,
+                       return_sum: bool = False):
+    """LayerNorm(x + residual) with the sum kept in fp32 on chip; the normalised value is rounded
+    to x's dtype before the affine part, as the reference's fused module does. Optionally also
+    returns the summed residual stream rounded to x's dtype."""
+    dev = _need_cuda(x, residual, weight, bias)
+    if residual.shape != x.shape or residual.dtype != x.dtype:
+        raise ValueError("residual must have the shape and dtype of x")
+    wb_dtype = weight.dtype if weight is not None else (bias.dtype if bias is not None else x.dtype)
+    w = weight.detach().contiguous() if weight is not None else None
+    b = bias.detach().to(wb_dtype).contiguous() if bias is not None else None
+    for t in (w, b):
+        if t is not None and t.numel() != x.shape[-1]:
+            raise ValueError("weight/bias size does not match the normalised dim")
+    x2, r2 = _rows(x), _rows(residual)
+    y = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=dev)
+    s = torch.empty_like(y) if return_sum else None
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_residual_layernorm_fwd(
+            _ptr(x2), _ptr(r2), _ptr(w), _ptr(b), _ptr(y), _ptr(s), None, None, x2.shape[0],
+            x2.shape[1], _row_stride(x2), _row_stride(r2), x2.shape[1], x2.shape[1], float(eps),
+            _code(x2), _DTYPE_CODE[wb_dtype], _stream(dev))
+    _lib.check("trx_residual_layernorm_fwd", rc)
+    _count()
+    y = y.view(x.shape)
+    return (y, s.view(x.shape)) if return_sum else y
+
+
 def residual_rmsnorm_quantize(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
                               eps: float = 1e-6, return_sum: bool = False):
     """int8 codes and scales of RMSNorm(x + residual); equals
