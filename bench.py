@@ -197,6 +197,14 @@ def bench_ops(device, pk):
         [lambda a=a: ops.rmsnorm(a, w, 1e-6) for a in acts])
     hbm("layernorm_bf16_32768x4096", R_ * C_ * 4 + 4 * C_,
         [lambda a=a: ops.layernorm(a, w, b, 1e-5) for a in acts])
+    # backward of the norms: read x and dy, write dx (6 B per element); dW / db via per-CTA fp32
+    # partial sums and a second, small kernel (both inside the timed graph)
+    hbm("rmsnorm_bwd_bf16_32768x4096", R_ * C_ * 6 + 4 * C_,
+        [lambda a=a, d=d: ops.rmsnorm_backward(d, a, w, 1e-6)
+         for a, d in ((acts[0], acts[1]), (acts[1], acts[0]))])
+    hbm("layernorm_bwd_bf16_32768x4096", R_ * C_ * 6 + 6 * C_,
+        [lambda a=a, d=d: ops.layernorm_backward(d, a, w, 1e-5)
+         for a, d in ((acts[0], acts[1]), (acts[1], acts[0]))])
     hbm("rmsnorm_quant_i8_32768x4096", BYTES_FUSED,
         [lambda a=a: ops.rmsnorm_quantize(a, w, 1e-6) for a in acts])
     # residual forms (the step either side of the norm in a decoder layer), new residual stream
@@ -232,7 +240,11 @@ def bench_ops(device, pk):
     xg = [rnd(16384, 22016) for _ in range(2)]
     for act in ("swiglu", "geglu", "reglu"):
         hbm(f"{act}_16384x11008", 16384 * 11008 * 6, [lambda x=x, a=act: ops.glu(x, a) for x in xg])
-    del xg
+    dyg = rnd(16384, 11008)
+    for act in ("swiglu", "geglu", "reglu"):  # backward: read dy, up, gate; write dup, dgate
+        hbm(f"{act}_bwd_16384x11008", 16384 * 11008 * 10,
+            [lambda x=x, a=act: ops.glu_backward(dyg, x, a) for x in xg])
+    del xg, dyg
     torch.cuda.empty_cache()
     # attention (cfg: q[16,4096,32,128], kv[16,4096,8,128])
     B, S, H, Hk, D = 16, 4096, 32, 8, 128

@@ -204,6 +204,53 @@ int trx_glu_fwd(const void* up, const void* gate, void* y, int64_t R, int64_t H,
                 int64_t up_row_stride, int64_t gate_row_stride, int64_t y_row_stride, int act,
                 int dtype, void* stream);
 
+/*
+ * Backward of the GLUs: dup = dy * act(gate), dgate = dy * up * act'(gate), fp32 math, one
+ * rounding per output. Every tensor has its own row stride, so dup / dgate may be the two halves
+ * of a concatenated (R, 2H) gradient.
+ * Replaces TritonSwiGLUFunction.backward (trinix/kernels/swigelu_kernel.py:154-180, kernel
+ * :47-91) and the GeGLU / ReGLU backward kernels (trinix/kernels/geglu_kernel.py:53-108,
+ * trinix/kernels/reglu_kernel.py:45-87).
+ */
+int trx_glu_bwd(const void* dy, const void* up, const void* gate, void* dup, void* dgate,
+                int64_t R, int64_t H, int64_t dy_row_stride, int64_t up_row_stride,
+                int64_t gate_row_stride, int64_t dup_row_stride, int64_t dgate_row_stride, int act,
+                int dtype, void* stream);
+
+/*
+ * Bytes of device workspace the norm backward entry points need for R rows of C columns: two
+ * (P, C) fp32 blocks of per-CTA column sums (P <= 1024, bounded so a block stays <= 16 MiB) plus
+ * (R, 2) fp32 row statistics. Contents on entry are irrelevant; nothing is kept between calls.
+ */
+size_t trx_norm_bwd_workspace_bytes(int64_t R, int64_t C);
+
+/*
+ * RMSNorm backward. With n = x * rsqrt(mean(x^2) + eps) (recomputed from x, nothing saved by the
+ * forward is needed) and g = dy * w:  dx = rstd * (g - n * mean(g * n)),  dw = sum_rows dy * n
+ * (fp32 sums in a fixed order: deterministic for a given shape and device; stored in w_dtype).
+ * dw_or_null == NULL skips the weight gradient.
+ * Replaces TritonRMSNormFunction.backward (trinix/kernels/rmsnorm_kernel.py:270-321; kernels
+ * rmsnorm_backward_dx_fused :65-147 with its lock-guarded accumulation, rmsnorm_backward_dw
+ * :151-194).
+ */
+int trx_rmsnorm_bwd(const void* dy, const void* x, const void* w, void* dx, void* dw_or_null,
+                    int64_t R, int64_t C, int64_t dy_row_stride, int64_t x_row_stride,
+                    int64_t dx_row_stride, float eps, int x_dtype, int w_dtype, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/*
+ * LayerNorm backward. n = (x - mean) * rstd, g = dy * w (w == NULL: g = dy):
+ *   dx = rstd * (g - mean(g) - n * mean(g * n)),  dw = sum_rows dy * n,  db = sum_rows dy.
+ * dw_or_null / db_or_null == NULL skip that gradient.
+ * Replaces TritonLayerNormFunction.backward (trinix/kernels/layernorm_kernel.py:298-353; kernels
+ * layernorm_backward_dx_fused :71-164, layernorm_backward_dwdb :168-221).
+ */
+int trx_layernorm_bwd(const void* dy, const void* x, const void* w_or_null, void* dx,
+                      void* dw_or_null, void* db_or_null, int64_t R, int64_t C,
+                      int64_t dy_row_stride, int64_t x_row_stride, int64_t dx_row_stride, float eps,
+                      int x_dtype, int wb_dtype, void* workspace, size_t workspace_bytes,
+                      void* stream);
+
 /* Bytes of zero-initialised device workspace trx_attn_fwd needs (status word + scheduler state). */
 size_t trx_attn_workspace_bytes(void);
 

@@ -162,5 +162,55 @@ with torch.no_grad():
     put("resln_y_f32w", mlr32(xl2, rl2))                   # fp32 parameters: promoted to fp32
     put("resln_y_f32", mlr32(xl2.float(), rl2.float()))    # fp32 activations
 
+# --- gradients through the reference's PyTorch backend (own generator)
+g4 = torch.Generator().manual_seed(4)
+
+
+for tag, dt in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+    xg_ = torch.randn(12, 640, generator=g4).to(dt)
+    dy_ = torch.randn(12, 640, generator=g4).to(dt)
+    wg_ = (1 + 0.1 * torch.randn(640, generator=g4)).to(dt)
+    bg_ = (0.1 * torch.randn(640, generator=g4)).to(dt)
+    mr_ = FastRMSNorm(640, eps=1e-6, use_triton=False).to(dt)
+
+    # the module's own forward, with its weight parameter as the leaf
+    mr_.weight.data.copy_(wg_)
+    xl_ = xg_.detach().clone().requires_grad_(True)
+    out_ = mr_(xl_)
+    dx_, dw_ = torch.autograd.grad(out_, [xl_, mr_.weight], dy_.to(out_.dtype))
+    put(f"bwd_rms_{tag}_x", xg_); put(f"bwd_rms_{tag}_dy", dy_); put(f"bwd_rms_{tag}_w", wg_)
+    put(f"bwd_rms_{tag}_dx", dx_); put(f"bwd_rms_{tag}_dw", dw_)
+
+    ml_ = FastLayerNorm(640, eps=1e-5, use_triton=False).to(dt)
+    ml_.weight.data.copy_(wg_); ml_.bias.data.copy_(bg_)
+    xl_ = xg_.detach().clone().requires_grad_(True)
+    out_ = ml_(xl_)
+    dx_, dw_, db_ = torch.autograd.grad(out_, [xl_, ml_.weight, ml_.bias], dy_.to(out_.dtype))
+    put(f"bwd_ln_{tag}_b", bg_)
+    put(f"bwd_ln_{tag}_dx", dx_); put(f"bwd_ln_{tag}_dw", dw_); put(f"bwd_ln_{tag}_db", db_)
+
+    xu_ = (torch.randn(10, 2 * 160, generator=g4) * 2).to(dt)
+    dyu_ = torch.randn(10, 160, generator=g4).to(dt)
+    put(f"bwd_glu_{tag}_x", xu_); put(f"bwd_glu_{tag}_dy", dyu_)
+    for name, cls in (("swiglu", FastSwiGLU), ("geglu", FastGeGLU), ("reglu", FastReGLU)):
+        xl_ = xu_.detach().clone().requires_grad_(True)
+        out_ = cls(160, use_triton=False)(xl_)
+        (dxu_,) = torch.autograd.grad(out_, [xl_], dyu_.to(out_.dtype))
+        put(f"bwd_{name}_{tag}_dx", dxu_)
+
+# RoPE: gradients of apply_rotary_pos_emb with respect to q and k (bf16 tables, built from q)
+rope_b = FastRoPEPositionEmbedding(64, 2048, 10000.0, use_triton=False)
+qb_ = torch.randn(2, 24, 4, 64, generator=g4).bfloat16()
+kb_ = torch.randn(2, 24, 2, 64, generator=g4).bfloat16()
+gq_ = torch.randn(2, 24, 4, 64, generator=g4).bfloat16()
+gk_ = torch.randn(2, 24, 2, 64, generator=g4).bfloat16()
+cosb_, sinb_ = rope_b(qb_, seq_len=24)
+ql_ = qb_.detach().clone().requires_grad_(True)
+kl_ = kb_.detach().clone().requires_grad_(True)
+qo_, ko_ = rope_b.apply_rotary_pos_emb(ql_, kl_, cosb_, sinb_)
+dq_, dk_ = torch.autograd.grad([qo_, ko_], [ql_, kl_], [gq_.to(qo_.dtype), gk_.to(ko_.dtype)])
+put("bwd_rope_gq", gq_); put("bwd_rope_gk", gk_); put("bwd_rope_cos", cosb_); put("bwd_rope_sin", sinb_)
+put("bwd_rope_dq", dq_); put("bwd_rope_dk", dk_)
+
 np.savez_compressed(OUT, **vec)
 print("wrote", OUT, os.path.getsize(OUT), "bytes;", len(vec), "arrays; trinix", trinix.__version__)

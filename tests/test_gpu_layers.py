@@ -53,14 +53,19 @@ def test_modules_route_to_kernels_above_thresholds(cuda, monkeypatch):
     assert len(rope_calls) == 1  # S <= 512 stays on torch, as in the reference
 
 
-def test_forward_only_autograd_contract(cuda):
+def test_autograd_contract(cuda):
+    """Norms, GLUs and RoPE are differentiable through the backward kernels; the fused forms (and
+    attention) are forward only and say so instead of silently producing no gradient."""
     m = T.FastRMSNorm(4096).to(cuda).bfloat16()
     x = torch.randn(4, 4096, device=cuda, dtype=torch.bfloat16)
-    y = m(x)  # weight requires grad and grad mode is on: forward still works
-    with pytest.raises(NotImplementedError):
-        y.float().sum().backward()
+    y = m(x)  # weight requires grad and grad mode is on
+    y.float().sum().backward()
+    assert m.weight.grad is not None and m.weight.grad.shape == (4096,)
     with torch.no_grad():
         assert m(x).grad_fn is None
+    f = T.FastFusedResidualRMSNorm(4096).to(cuda).bfloat16()
+    with pytest.raises(NotImplementedError):
+        f(x, x).float().sum().backward()
 
 
 def _layer_weights(E, Hq, Hkv, FF, seed=0):

@@ -141,3 +141,48 @@ def test_gqa_module_composition():
     a = R.attention_variant_ref(q, k, v, D ** -0.5, True)
     out = F.linear(a.reshape(B, S, -1), G("gqa_o_proj"))
     torch.testing.assert_close(out, G("gqa_out"), rtol=1e-5, atol=1e-6)
+
+
+def _close_grad(a, b, tag):
+    """Gradient from the restated forward under autograd against the reference's own."""
+    assert a.dtype == b.dtype and a.shape == b.shape
+    if tag == "f32":
+        torch.testing.assert_close(a, b, rtol=2e-5, atol=2e-6)
+    else:  # same ops in the same order; a host's vector units may flip a last bit
+        assert int(bf16_ulps(a, b).max()) <= 2
+
+
+@pytest.mark.parametrize("tag", ["f32", "bf16"])
+def test_gradients_of_the_restated_forwards_match_the_reference(tag):
+    x, dy, w, b = (G(f"bwd_rms_{tag}_x"), G(f"bwd_rms_{tag}_dy"), G(f"bwd_rms_{tag}_w"),
+                   G(f"bwd_ln_{tag}_b"))
+    dx, dw = R.autograd_ref(lambda a, ww: R.rmsnorm_ref(a, ww, 1e-6), [x, w], dy)
+    _close_grad(dx, G(f"bwd_rms_{tag}_dx"), tag)
+    _close_grad(dw, G(f"bwd_rms_{tag}_dw"), tag)
+    # ATen's CPU layer-norm backward splits the rows over its threads and adds the per-thread
+    # partial sums of dgamma / dbeta in the storage dtype, so in bf16 they depend on the thread
+    # count; the vectors were generated on one thread
+    threads = torch.get_num_threads()
+    torch.set_num_threads(1)
+    try:
+        dx, dw, db = R.autograd_ref(lambda a, ww, bb: R.layernorm_ref(a, ww, bb, 1e-5),
+                                    [x, w, b], dy)
+    finally:
+        torch.set_num_threads(threads)
+    _close_grad(dx, G(f"bwd_ln_{tag}_dx"), tag)
+    _close_grad(dw, G(f"bwd_ln_{tag}_dw"), tag)
+    _close_grad(db, G(f"bwd_ln_{tag}_db"), tag)
+    xg, dyg = G(f"bwd_glu_{tag}_x"), G(f"bwd_glu_{tag}_dy")
+    for name, fn in (("swiglu", R.swiglu_ref), ("geglu", R.geglu_ref), ("reglu", R.reglu_ref)):
+        (dxg,) = R.autograd_ref(fn, [xg], dyg)
+        _close_grad(dxg, G(f"bwd_{name}_{tag}_dx"), tag)
+
+
+def test_rope_gradient_is_the_inverse_rotation():
+    cos, sin = G("bwd_rope_cos"), G("bwd_rope_sin")
+    gq, gk = G("bwd_rope_gq"), G("bwd_rope_gk")
+    q0, k0 = torch.zeros_like(gq), torch.zeros_like(gk)
+    dq, dk, _, _ = R.autograd_ref(R.rope_ref, [q0, k0, cos, sin], (gq, gk))
+    assert int(bf16_ulps(dq, G("bwd_rope_dq")).max()) <= 1
+    assert int(bf16_ulps(dk, G("bwd_rope_dk")).max()) <= 1
+

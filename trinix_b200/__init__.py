@@ -41,14 +41,17 @@ from .ops import (
     attention_status,
     dequantize_rowwise,
     glu,
+    glu_backward,
     glu_pair,
     layernorm,
+    layernorm_backward,
     quantize_rowwise,
     residual_layernorm,
     residual_rmsnorm,
     residual_rmsnorm_quantize,
     rmsnorm,
     rmsnorm_activation,
+    rmsnorm_backward,
     rmsnorm_quantize,
     rope,
 )

@@ -48,6 +48,15 @@ SIGNATURES = {
                              c_int64, c_int, c_int, c_int, c_void_p]),
     "trx_glu_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                             c_int64, c_int, c_int, c_void_p]),
+    "trx_glu_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                            c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "trx_norm_bwd_workspace_bytes": (c_size_t, [c_int64, c_int64]),
+    "trx_rmsnorm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                c_int64, c_int64, c_int64, c_float, c_int, c_int, c_void_p,
+                                c_size_t, c_void_p]),
+    "trx_layernorm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int,
+                                  c_int, c_void_p, c_size_t, c_void_p]),
     "trx_attn_workspace_bytes": (c_size_t, []),
     "trx_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                              c_int64, c_int64, c_int64, c_int64, c_int64, I64x3, I64x3, I64x3,

@@ -6,8 +6,12 @@ object with the same two static methods is a drop-in. Here `apply` runs the sm_1
 kernel through the C ABI. The classes keep the reference's `Triton*` names because that
 is the interface being replaced; nothing in this package uses Triton.
 
-Forward only: outputs are attached to the autograd graph so that a later `.backward()`
-fails with a clear error instead of silently producing no gradient.
+RMSNorm, LayerNorm, RoPE and the GLUs are differentiable: their autograd functions run the
+backward kernels of the same library (the reference's Triton*Function.backward methods,
+e.g. trinix/kernels/rmsnorm_kernel.py:270-321). Attention, the fused forms and the int8 ops are
+forward only, as attention is in the reference (TritonAttentionKernel has no backward): their
+outputs are attached to the autograd graph so that a later `.backward()` fails with a clear
+error instead of silently producing no gradient.
 """
 from __future__ import annotations
 
@@ -37,13 +41,86 @@ class _ForwardOnly(torch.autograd.Function):
         )
 
 
-def _run(fn, *args):
-    needs_graph = torch.is_grad_enabled() and any(
+def _needs_graph(*args) -> bool:
+    return torch.is_grad_enabled() and any(
         isinstance(a, torch.Tensor) and a.requires_grad for a in args
     )
-    if needs_graph:
+
+
+def _run(fn, *args):
+    if _needs_graph(*args):
         return _ForwardOnly.apply(fn, *args)
     return fn(*args)
+
+
+class _RMSNormFn(torch.autograd.Function):
+    """Counterpart of TritonRMSNormFunction (trinix/kernels/rmsnorm_kernel.py:197-321). Saves x and
+    w only: the backward kernel recomputes the row statistics."""
+
+    @staticmethod
+    def forward(ctx, X, W, eps):
+        ctx.save_for_backward(X, W)
+        ctx.eps = eps
+        return ops.rmsnorm(X, W, eps)
+
+    @staticmethod
+    def backward(ctx, dY):
+        X, W = ctx.saved_tensors
+        dx, dw = ops.rmsnorm_backward(dY, X, W, ctx.eps, need_dw=ctx.needs_input_grad[1])
+        return dx, dw, None
+
+
+class _LayerNormFn(torch.autograd.Function):
+    """Counterpart of TritonLayerNormFunction (trinix/kernels/layernorm_kernel.py:224-353)."""
+
+    @staticmethod
+    def forward(ctx, X, W, b, eps):
+        ctx.save_for_backward(X, W)
+        ctx.eps = eps
+        ctx.bias_dtype = b.dtype if b is not None else None
+        return ops.layernorm(X, W, b, eps)
+
+    @staticmethod
+    def backward(ctx, dY):
+        X, W = ctx.saved_tensors
+        need_db = ctx.bias_dtype is not None and ctx.needs_input_grad[2]
+        dx, dw, db = ops.layernorm_backward(dY, X, W, ctx.eps, need_dw=ctx.needs_input_grad[1],
+                                            need_db=need_db)
+        if db is not None and db.dtype != ctx.bias_dtype:
+            db = db.to(ctx.bias_dtype)
+        return dx, dw, db, None
+
+
+class _GLUFn(torch.autograd.Function):
+    """Counterpart of Triton{SwiGLU,GeGLU,ReGLU}Function (e.g.
+    trinix/kernels/swigelu_kernel.py:94-180): saves the input, one backward kernel."""
+
+    @staticmethod
+    def forward(ctx, X, act):
+        ctx.save_for_backward(X)
+        ctx.act = act
+        return ops.glu(X, act)
+
+    @staticmethod
+    def backward(ctx, dY):
+        (X,) = ctx.saved_tensors
+        return ops.glu_backward(dY, X, ctx.act), None
+
+
+class _RoPEFn(torch.autograd.Function):
+    """Counterpart of TritonRoPEFunction (trinix/kernels/rope_kernel.py:133-177): the backward is
+    the rotation by the negated angle, applied to both gradients in one launch."""
+
+    @staticmethod
+    def forward(ctx, q, k, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        return ops.rope(q, k, cos, sin)
+
+    @staticmethod
+    def backward(ctx, grad_q, grad_k):
+        cos, sin = ctx.saved_tensors
+        dq, dk = ops.rope(grad_q, grad_k, cos, sin, inverse=True)
+        return dq, dk, None, None
 
 
 class TritonRMSNormKernel:
@@ -55,7 +132,9 @@ class TritonRMSNormKernel:
 
     @staticmethod
     def apply(X: torch.Tensor, W: torch.Tensor, eps: float) -> torch.Tensor:
-        return _run(lambda x, w: ops.rmsnorm(x, w, eps), X, W)
+        if _needs_graph(X, W):
+            return _RMSNormFn.apply(X, W, eps)
+        return ops.rmsnorm(X, W, eps)
 
 
 class TritonLayerNormKernel:
@@ -68,7 +147,9 @@ class TritonLayerNormKernel:
     @staticmethod
     def apply(X: torch.Tensor, W: Optional[torch.Tensor], b: Optional[torch.Tensor],
               eps: float) -> torch.Tensor:
-        return _run(lambda x, w, bb: ops.layernorm(x, w, bb, eps), X, W, b)
+        if _needs_graph(X, W, b):
+            return _LayerNormFn.apply(X, W, b, eps)
+        return ops.layernorm(X, W, b, eps)
 
 
 class TritonFusedResidualRMSNormKernel:
@@ -121,7 +202,9 @@ class TritonRoPEKernel:
     @staticmethod
     def apply(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor,
               sin: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-        return _run(lambda a, b, c, s: ops.rope(a, b, c, s), q, k, cos, sin)
+        if _needs_graph(q, k):
+            return _RoPEFn.apply(q, k, cos, sin)
+        return ops.rope(q, k, cos, sin)
 
 
 class TritonSwiGLUKernel:
@@ -133,7 +216,9 @@ class TritonSwiGLUKernel:
 
     @staticmethod
     def apply(X: torch.Tensor) -> torch.Tensor:
-        return _run(lambda x: ops.glu(x, "swiglu"), X)
+        if _needs_graph(X):
+            return _GLUFn.apply(X, "swiglu")
+        return ops.glu(X, "swiglu")
 
 
 class TritonGeGLUKernel:
@@ -145,7 +230,9 @@ class TritonGeGLUKernel:
 
     @staticmethod
     def apply(X: torch.Tensor) -> torch.Tensor:
-        return _run(lambda x: ops.glu(x, "geglu"), X)
+        if _needs_graph(X):
+            return _GLUFn.apply(X, "geglu")
+        return ops.glu(X, "geglu")
 
 
 class TritonReGLUKernel:
@@ -157,7 +244,9 @@ class TritonReGLUKernel:
 
     @staticmethod
     def apply(X: torch.Tensor) -> torch.Tensor:
-        return _run(lambda x: ops.glu(x, "reglu"), X)
+        if _needs_graph(X):
+            return _GLUFn.apply(X, "reglu")
+        return ops.glu(X, "reglu")
 
 
 class TritonAttentionKernel:

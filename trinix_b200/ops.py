@@ -356,6 +356,84 @@ def glu_pair(up: torch.Tensor, gate: torch.Tensor, act: str) -> torch.Tensor:
     return y.view(up.shape)
 
 
+# ----------------------------------------------------------------------------- backward
+def glu_backward(dy: torch.Tensor, x: torch.Tensor, act: str) -> torch.Tensor:
+    """Gradient of glu(x, act) with respect to x (..., 2H), given dy (..., H): the two halves
+    dy * act(gate) and dy * up * act'(gate) written into one tensor of x's shape."""
+    dev = _need_cuda(dy, x)
+    h = x.shape[-1] // 2
+    if x.shape[-1] % 2 or dy.shape != x.shape[:-1] + (h,) or dy.dtype != x.dtype:
+        raise ValueError("dy must have x's leading shape, half its last dimension and its dtype")
+    x2, dy2 = _rows(x), _rows(dy)
+    dx = torch.empty((x2.shape[0], 2 * h), dtype=x.dtype, device=dev)
+    rs = _row_stride(x2)
+    es = x2.element_size()
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_glu_bwd(
+            _ptr(dy2), ctypes.c_void_p(x2.data_ptr()), ctypes.c_void_p(x2.data_ptr() + h * es),
+            ctypes.c_void_p(dx.data_ptr()), ctypes.c_void_p(dx.data_ptr() + h * es), x2.shape[0], h,
+            _row_stride(dy2), rs, rs, 2 * h, 2 * h, GLU_ACTS[act], _code(x2), _stream(dev))
+    _lib.check("trx_glu_bwd", rc)
+    _count()
+    return dx.view(x.shape)
+
+
+def _norm_bwd_workspace(rows: int, cols: int, dev: torch.device) -> torch.Tensor:
+    n = int(_lib.load().trx_norm_bwd_workspace_bytes(rows, cols))
+    return torch.empty(n, dtype=torch.uint8, device=dev)
+
+
+def rmsnorm_backward(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
+                     need_dw: bool = True):
+    """(dx, dw) of rmsnorm(x, weight, eps) given dy; dw is None when need_dw is False. The row
+    statistics are recomputed from x; dw is summed in fp32 in a fixed order."""
+    dev = _need_cuda(dy, x, weight)
+    if dy.shape != x.shape or dy.dtype != x.dtype:
+        raise ValueError("dy must have the shape and dtype of x")
+    if weight.numel() != x.shape[-1]:
+        raise ValueError(f"weight has {weight.numel()} elements, rows have {x.shape[-1]}")
+    x2, dy2 = _rows(x), _rows(dy)
+    w = weight.detach().contiguous()
+    dx = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=dev)
+    dw = torch.empty(x2.shape[1], dtype=w.dtype, device=dev) if need_dw else None
+    ws = _norm_bwd_workspace(x2.shape[0], x2.shape[1], dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_rmsnorm_bwd(
+            _ptr(dy2), _ptr(x2), _ptr(w), _ptr(dx), _ptr(dw), x2.shape[0], x2.shape[1],
+            _row_stride(dy2), _row_stride(x2), x2.shape[1], float(eps), _code(x2), _code(w),
+            _ptr(ws), ws.numel(), _stream(dev))
+    _lib.check("trx_rmsnorm_bwd", rc)
+    _count()
+    return dx.view(x.shape), (dw.view(weight.shape) if need_dw else None)
+
+
+def layernorm_backward(dy: torch.Tensor, x: torch.Tensor, weight: Optional[torch.Tensor],
+                       eps: float = 1e-5, need_dw: bool = True, need_db: bool = True):
+    """(dx, dw, db) of layernorm(x, weight, bias, eps) given dy; weight may be None (then dw is
+    None); db is returned in the weight's dtype (x's dtype without a weight)."""
+    dev = _need_cuda(dy, x, weight)
+    if dy.shape != x.shape or dy.dtype != x.dtype:
+        raise ValueError("dy must have the shape and dtype of x")
+    if weight is not None and weight.numel() != x.shape[-1]:
+        raise ValueError("weight size does not match the normalised dim")
+    x2, dy2 = _rows(x), _rows(dy)
+    w = weight.detach().contiguous() if weight is not None else None
+    p_dtype = w.dtype if w is not None else x.dtype
+    need_dw = need_dw and w is not None
+    dx = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=dev)
+    dw = torch.empty(x2.shape[1], dtype=p_dtype, device=dev) if need_dw else None
+    db = torch.empty(x2.shape[1], dtype=p_dtype, device=dev) if need_db else None
+    ws = _norm_bwd_workspace(x2.shape[0], x2.shape[1], dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().trx_layernorm_bwd(
+            _ptr(dy2), _ptr(x2), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db), x2.shape[0], x2.shape[1],
+            _row_stride(dy2), _row_stride(x2), x2.shape[1], float(eps), _code(x2),
+            _DTYPE_CODE[p_dtype], _ptr(ws), ws.numel(), _stream(dev))
+    _lib.check("trx_layernorm_bwd", rc)
+    _count()
+    return dx.view(x.shape), dw, db
+
+
 # ----------------------------------------------------------------------------- attention
 _workspaces: dict = {}
 
