@@ -401,6 +401,14 @@ def profile_case(name: str):
             ops.layernorm(acts[i % 2], w, b, 1e-5)
             ops.rope(q, k, cos, sin)
             ops.glu(xg, "swiglu")
+    elif name == "backward":
+        acts = [rnd(ACT_ROWS, ACT_SHAPE[2]) for _ in range(2)]
+        w = torch.ones(ACT_SHAPE[2], device=device, dtype=torch.bfloat16)
+        xg, dyg = rnd(8192, 22016), rnd(8192, 11008)
+        for i in range(3):
+            ops.rmsnorm_backward(acts[(i + 1) % 2], acts[i % 2], w, 1e-6)
+            ops.layernorm_backward(acts[(i + 1) % 2], acts[i % 2], w, 1e-5)
+            ops.glu_backward(dyg, xg, "swiglu")
     else:
         q, k, v = rnd(2, 4096, 32, 128), rnd(2, 4096, 8, 128), rnd(2, 4096, 8, 128)
         for _ in range(4):
@@ -418,7 +426,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-kernel table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--profile-case", choices=["int8", "stream", "attention"],
+    ap.add_argument("--profile-case", choices=["int8", "stream", "backward", "attention"],
                     help="launch a few kernels of one family eagerly and exit (for ncu captures)")
     args = ap.parse_args()
     if args.profile_case:

@@ -251,6 +251,38 @@ int trx_layernorm_bwd(const void* dy, const void* x, const void* w_or_null, void
                       int x_dtype, int wb_dtype, void* workspace, size_t workspace_bytes,
                       void* stream);
 
+/*
+ * Backward of the residual forms: the normalised row is the fp32 sum x + residual, exactly as in
+ * trx_residual_rmsnorm_fwd / trx_residual_layernorm_fwd; d/dx and d/dresidual are the same tensor,
+ * written once to dx. Otherwise as trx_rmsnorm_bwd / trx_layernorm_bwd (same workspace).
+ * Replace TritonFusedResidualRMSNormFunction.backward
+ * (trinix/kernels/fused/residual_rmsnorm_kernel.py:251-303; kernels :77-205) and
+ * TritonFusedResidualLayerNormFunction.backward
+ * (trinix/kernels/fused/residual_layernorm_kernel.py:278-335; kernels :83-225).
+ */
+int trx_residual_rmsnorm_bwd(const void* dy, const void* x, const void* residual, const void* w,
+                             void* dx, void* dw_or_null, int64_t R, int64_t C,
+                             int64_t dy_row_stride, int64_t x_row_stride, int64_t res_row_stride,
+                             int64_t dx_row_stride, float eps, int x_dtype, int w_dtype,
+                             void* workspace, size_t workspace_bytes, void* stream);
+int trx_residual_layernorm_bwd(const void* dy, const void* x, const void* residual,
+                               const void* w_or_null, void* dx, void* dw_or_null, void* db_or_null,
+                               int64_t R, int64_t C, int64_t dy_row_stride, int64_t x_row_stride,
+                               int64_t res_row_stride, int64_t dx_row_stride, float eps,
+                               int x_dtype, int wb_dtype, void* workspace, size_t workspace_bytes,
+                               void* stream);
+
+/*
+ * Backward of act(RMSNorm(x)) (trx_rmsnorm_act_fwd): with z = w * n the upstream gradient becomes
+ * dy * act'(z), then as trx_rmsnorm_bwd (same workspace). act is one of TRX_ACT_*.
+ * Replaces TritonFusedRMSNormActivationFunction.backward
+ * (trinix/kernels/fused/rmsnorm_activation_kernel.py:280-330; kernels :81-233).
+ */
+int trx_rmsnorm_act_bwd(const void* dy, const void* x, const void* w, void* dx, void* dw_or_null,
+                        int64_t R, int64_t C, int64_t dy_row_stride, int64_t x_row_stride,
+                        int64_t dx_row_stride, float eps, int act, int x_dtype, int w_dtype,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
 /* Bytes of zero-initialised device workspace trx_attn_fwd needs (status word + scheduler state). */
 size_t trx_attn_workspace_bytes(void);
 

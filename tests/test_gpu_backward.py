@@ -2,8 +2,10 @@
 backend, through the kernel classes' autograd functions and the C ABI.
 
 Two yardsticks. (1) The upcast oracle: autograd through the restated forward on `.double()`
-inputs — the tighter truth; a 16-bit kernel result may differ from it by its one output rounding
-(half an ulp: 2^-9 relative for bf16, 2^-12 for fp16) plus fp32 summation order. (2) The
+inputs (LayerNorm and the GLUs then run in float64; the RMSNorm-family forwards cast to fp32
+internally, as the reference's do, so for them this is the fp32 evaluation on exact inputs) — the
+tighter truth; a 16-bit kernel result may differ from it by its one output rounding (half an ulp:
+2^-9 relative for bf16, 2^-12 for fp16) plus fp32 summation order. (2) The
 reference's own 16-bit autograd, which rounds every intermediate to the storage dtype (and, for
 LayerNorm's dgamma / dbeta on CPU, adds partial sums in that dtype): looser by construction. A
 norm's dx is a difference of terms of the size of the tensor's rms, each carrying such a rounding,
@@ -52,13 +54,15 @@ def test_norm_gradients_golden(cuda, tag):
     _, (dx, dw) = _run_backward(lambda a, ww: T.TritonRMSNormKernel.apply(a, ww, 1e-6), [x, w], dy, cuda)
     assert dx.dtype == x.dtype and dw.dtype == w.dtype
     close = (lambda a, b: rel_err(a, b) <= 2e-5) if tag == "f32" else _chain_close
+    # dW / db are fp32 sums over the rows: 1e-4 of max(|ref|, 1 % rms), see the shape test
+    close_sum = (lambda a, b: rel_err(a, b) <= 1e-4) if tag == "f32" else _chain_close
     assert close(dx, G(f"bwd_rms_{tag}_dx"))
-    assert close(dw, G(f"bwd_rms_{tag}_dw"))
+    assert close_sum(dw, G(f"bwd_rms_{tag}_dw"))
     _, (dx, dw, db) = _run_backward(lambda a, ww, bb: T.TritonLayerNormKernel.apply(a, ww, bb, 1e-5),
                                     [x, w, b], dy, cuda)
     assert close(dx, G(f"bwd_ln_{tag}_dx"))
     if tag == "f32":
-        assert close(dw, G(f"bwd_ln_{tag}_dw")) and close(db, G(f"bwd_ln_{tag}_db"))
+        assert close_sum(dw, G(f"bwd_ln_{tag}_dw")) and close_sum(db, G(f"bwd_ln_{tag}_db"))
     else:
         # ATen's CPU kernel adds the rows' contributions to dgamma / dbeta in bf16: its own error
         # is about 1 % of the vector's rms, so the bound against it is 5e-2 (|b| + rms(b)); the
@@ -136,6 +140,71 @@ def test_norm_backward_shapes(cuda, rows, cols, dtype):
     assert rel_err(db.cpu().double(), dy.double().sum(0)) <= tol_sum
 
 
+@pytest.mark.parametrize("rows,cols,dtype", [(64, 4096, torch.bfloat16), (5, 1000, torch.bfloat16),
+                                             (7, 8192, torch.float16), (3, 4104, torch.float32),
+                                             (2, 40000, torch.bfloat16), (300, 512, torch.float32)])
+def test_residual_norm_backward(cuda, rows, cols, dtype):
+    """Residual forms: the gradient of norm(x + r) at the fp32 sum, one tensor for x and r, through
+    the fused kernel classes' autograd functions, against the float64 oracle."""
+    g = torch.Generator().manual_seed(rows * 13 + cols)
+    x = (torch.randn(rows, cols, generator=g) + 0.2).to(dtype)
+    r = (torch.randn(rows, cols, generator=g) * 2).to(dtype)
+    dy = torch.randn(rows, cols, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(cols, generator=g)).to(dtype)
+    b = (0.1 * torch.randn(cols, generator=g)).to(dtype)
+    tol, tol_sum = TOL32[dtype], max(TOL32[dtype], 1e-4)
+    _, (dx, dr, dw) = _run_backward(
+        lambda a, rr, ww: T.TritonFusedResidualRMSNormKernel.apply(a, rr, ww, 1e-6), [x, r, w], dy, cuda)
+    rx, rr_, rw = R.autograd_ref(lambda a, rr, ww: R.residual_rmsnorm_ref(a, rr, ww, 1e-6),
+                                 _f(x, r, w), dy.double())
+    assert torch.equal(dx, dr) and dx.dtype == dtype
+    assert rel_err(dx.double(), rx) <= tol and rel_err(dr.double(), rr_) <= tol
+    assert rel_err(dw.double(), rw) <= tol_sum
+    _, (dx, dr, dw, db) = _run_backward(
+        lambda a, rr, ww, bb: T.TritonFusedResidualLayerNormKernel.apply(a, rr, ww, bb, 1e-5),
+        [x, r, w, b], dy, cuda)
+    rx, rr_, rw, rb = R.autograd_ref(lambda a, rr, ww, bb: R.residual_layernorm_ref(a, rr, ww, bb, 1e-5),
+                                     _f(x, r, w, b), dy.double())
+    assert torch.equal(dx, dr)
+    assert rel_err(dx.double(), rx) <= tol
+    assert rel_err(dw.double(), rw) <= tol_sum and rel_err(db.double(), rb) <= tol_sum
+    # the same numbers as the unfused backward fed the rounded sum, where that sum is exact (fp32)
+    if dtype == torch.float32:
+        s = (x + r).to(cuda)
+        ux, uw = T.ops.rmsnorm_backward(dy.to(cuda), s, w.to(cuda), 1e-6)
+        fx, fw = T.ops.rmsnorm_backward(dy.to(cuda), x.to(cuda), w.to(cuda), 1e-6, residual=r.to(cuda))
+        assert torch.equal(ux, fx) and torch.equal(uw, fw)
+
+
+@pytest.mark.parametrize("act", ["mish", "quickgelu", "squared_relu"])
+@pytest.mark.parametrize("rows,cols,dtype", [(64, 4096, torch.bfloat16), (5, 1000, torch.bfloat16),
+                                             (7, 8192, torch.float16), (3, 4104, torch.float32),
+                                             (2, 40000, torch.float32)])
+def test_rmsnorm_activation_backward(cuda, act, rows, cols, dtype):
+    """act(RMSNorm(x)): the chain rule through the activation inside the norm's backward kernel,
+    through the fused kernel class's autograd function, against the float64 oracle."""
+    g = torch.Generator().manual_seed(rows * 7 + cols)
+    x = (torch.randn(rows, cols, generator=g) * 3).to(dtype)
+    dy = torch.randn(rows, cols, generator=g).to(dtype)
+    w = (1 + 0.2 * torch.randn(cols, generator=g)).to(dtype)
+    _, (dx, dw) = _run_backward(
+        lambda a, ww: T.TritonFusedRMSNormActivationKernel.apply(a, ww, 1e-6, act), [x, w], dy, cuda)
+    rx, rw = R.autograd_ref(lambda a, ww: R.rmsnorm_activation_ref(a, ww, 1e-6, act), _f(x, w),
+                            dy.double())
+    assert dx.dtype == dtype and dw.dtype == dtype
+    # fp32: dx = rstd (g - n mean(g n)) with |g| up to some 50 times the rms of dx here (inputs
+    # times 3, act' up to 2 z), so its fp32 rounding noise is 1e-4 of max(|ref|, 1 % rms) on both
+    # sides of the comparison
+    assert rel_err(dx.double(), rx) <= max(TOL32[dtype], 1e-4)
+    assert rel_err(dw.double(), rw) <= max(TOL32[dtype], 1e-4)
+    # saturation: huge normalised values times huge weights stay finite
+    xe = torch.tensor([[300.0, -300.0, 1.0, -1.0, 0.0, 2.0, -2.0, 5.0]]).to(dtype)
+    we = torch.full((8,), 100.0).to(dtype)
+    de, _ = T.ops.rmsnorm_backward(torch.ones(1, 8).to(dtype).to(cuda), xe.to(cuda), we.to(cuda),
+                                   1e-6, activation=act)
+    assert bool(torch.isfinite(de.float()).all())
+
+
 def test_norm_backward_is_deterministic_and_reads_strided_rows(cuda):
     g = torch.Generator().manual_seed(5)
     big = torch.randn(2048, 2 * 4096, generator=g).bfloat16().to(cuda)
@@ -197,6 +266,24 @@ def test_mirror_modules_train_through_the_kernels(cuda):
         assert rel_err(xl.grad.cpu(), xr.grad) <= 2e-5
         for (n1, p1), (_, p2) in zip(m.named_parameters(), ref.named_parameters()):
             assert rel_err(p1.grad.cpu(), p2.grad) <= 1e-4, n1  # fp32 sums over the rows
+    for make in (lambda: T.FastFusedResidualRMSNorm(4104, eps=1e-6),
+                 lambda: T.FastFusedResidualLayerNorm(4104, eps=1e-5)):
+        m = make().to(cuda)
+        assert m._check_triton_availability()
+        with torch.no_grad():
+            m.weight.copy_(1 + 0.1 * torch.randn(4104, generator=g))
+        res = torch.randn(2, 6, 4104, generator=g)
+        xl, rl = x.to(cuda).requires_grad_(True), res.to(cuda).requires_grad_(True)
+        m(xl, rl).backward(dy.to(cuda))
+        ref = make()
+        ref.load_state_dict({k: v.cpu() for k, v in m.state_dict().items()})
+        xr, rr = x.clone().requires_grad_(True), res.clone().requires_grad_(True)
+        ref._pytorch_forward(xr, rr).backward(dy)
+        # both sides are fp32 here (the reference module on the CPU is the yardstick)
+        assert rel_err(xl.grad.cpu(), xr.grad) <= 5e-5, rel_err(xl.grad.cpu(), xr.grad)
+        assert rel_err(rl.grad.cpu(), rr.grad) <= 5e-5
+        for (n1, p1), (_, p2) in zip(m.named_parameters(), ref.named_parameters()):
+            assert rel_err(p1.grad.cpu(), p2.grad) <= 1e-4, n1
     xg = torch.randn(3, 5, 2 * 640, generator=g)
     dyg = torch.randn(3, 5, 640, generator=g)
     for cls in (T.FastSwiGLU, T.FastGeGLU, T.FastReGLU):
@@ -204,7 +291,8 @@ def test_mirror_modules_train_through_the_kernels(cuda):
         cls(640)(xl).backward(dyg.to(cuda))
         xr = xg.clone().requires_grad_(True)
         cls(640, use_triton=False)(xr).backward(dyg)
-        assert rel_err(xl.grad.cpu(), xr.grad) <= 2e-5
+        # ATen's fp32 GELU-tanh backward carries a cancellation error of about 1e-4 of its own
+        assert rel_err(xl.grad.cpu(), xr.grad) <= (2e-4 if cls is T.FastGeGLU else 2e-5)
 
 
 def test_forward_only_ops_still_refuse_backward(cuda):

@@ -54,8 +54,8 @@ def test_modules_route_to_kernels_above_thresholds(cuda, monkeypatch):
 
 
 def test_autograd_contract(cuda):
-    """Norms, GLUs and RoPE are differentiable through the backward kernels; the fused forms (and
-    attention) are forward only and say so instead of silently producing no gradient."""
+    """Norms, GLUs and RoPE are differentiable through the backward kernels; attention is forward
+    only (as in the reference) and says so instead of silently producing no gradient."""
     m = T.FastRMSNorm(4096).to(cuda).bfloat16()
     x = torch.randn(4, 4096, device=cuda, dtype=torch.bfloat16)
     y = m(x)  # weight requires grad and grad mode is on
@@ -63,9 +63,9 @@ def test_autograd_contract(cuda):
     assert m.weight.grad is not None and m.weight.grad.shape == (4096,)
     with torch.no_grad():
         assert m(x).grad_fn is None
-    f = T.FastFusedResidualRMSNorm(4096).to(cuda).bfloat16()
+    q = torch.randn(1, 128, 2, 128, device=cuda, dtype=torch.bfloat16, requires_grad=True)
     with pytest.raises(NotImplementedError):
-        f(x, x).float().sum().backward()
+        T.TritonAttentionKernel.apply(q, q, q, causal=True).float().sum().backward()
 
 
 def _layer_weights(E, Hq, Hkv, FF, seed=0):

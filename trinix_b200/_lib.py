@@ -57,6 +57,16 @@ SIGNATURES = {
     "trx_layernorm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int,
                                   c_int, c_void_p, c_size_t, c_void_p]),
+    "trx_residual_rmsnorm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                         c_float, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "trx_residual_layernorm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                           c_int64, c_int64, c_float, c_int, c_int, c_void_p,
+                                           c_size_t, c_void_p]),
+    "trx_rmsnorm_act_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                    c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int, c_int,
+                                    c_void_p, c_size_t, c_void_p]),
     "trx_attn_workspace_bytes": (c_size_t, []),
     "trx_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                              c_int64, c_int64, c_int64, c_int64, c_int64, I64x3, I64x3, I64x3,

@@ -45,14 +45,16 @@ struct NormBwdParams {
   const void* dy;
   const void* x;
   const void* w;     // may be null (LayerNorm without affine part)
+  const void* res;   // may be null; otherwise the row is x + res (fp32 sum), dx serves both
   void* dx;
   float* dw_part;    // (P, C) fp32 or null
   float* db_part;    // (P, C) fp32 or null
   float* stats;      // (R, 2) fp32: mean, rstd (scalar path only)
   int64_t R, C;
-  int64_t dy_stride, x_stride, dx_stride;  // elements
+  int64_t dy_stride, x_stride, dx_stride, res_stride;  // elements
   float eps;
   int w_dtype;
+  int act;           // -1: plain norm; TRX_ACT_*: the upstream gradient is dy * act'(w * n)
 };
 
 // Sum of a float2 over the NT threads of a CTA; two alternating banks, one barrier.
@@ -75,6 +77,33 @@ __device__ __forceinline__ float2 block_sum2(float2 v, float2 (*red)[NT / 32], i
   return r;
 }
 
+// act'(z) for the activations of act(RMSNorm(x)): mish z tanh(softplus z), quickgelu
+// z sigmoid(1.702 z), squared ReLU max(z, 0)^2. With q = e^z (e^z + 2): tanh(softplus z) =
+// q / (q + 2) and 1 - tanh = 2 / (q + 2), so 1 - tanh^2 carries no cancellation; z is clamped at
+// 20 for the exponential (the derivative is 1 to fp32 precision beyond that).
+// FAST (16-bit tensors): hardware exponential and reciprocal.
+template <bool FAST>
+__device__ __forceinline__ float act_grad(int act, float z) {
+  auto ex = [](float v) { return FAST ? __expf(v) : expf(v); };
+  auto rcp = [](float v) { return FAST ? __fdividef(1.0f, v) : __fdiv_rn(1.0f, v); };
+  if (act == TRX_ACT_MISH) {
+    const float e = ex(fminf(z, 20.0f));
+    const float q = e * (e + 2.0f);
+    const float r = rcp(q + 2.0f);
+    const float th = q * r;
+    const float sg = e * rcp(1.0f + e);
+    return fmaf(z * sg, 2.0f * r * (1.0f + th), th);
+  }
+  if (act == TRX_ACT_QUICKGELU) {
+    const float a = 1.702f * z;
+    const float e = ex(-fabsf(a));
+    const float sp = rcp(1.0f + e), sm = e * sp;
+    const float s = a >= 0.0f ? sp : sm, t = a >= 0.0f ? sm : sp;
+    return s * fmaf(a, t, 1.0f);
+  }
+  return 2.0f * fmaxf(z, 0.0f);
+}
+
 template <bool LN, typename T, int VPT, int NT>
 __global__ void __launch_bounds__(NT, NT == 256 ? (LN ? TRX_BWD_MINB_LN : TRX_BWD_MINB_RMS) : 1) norm_bwd_kernel(const NormBwdParams p) {
   using P = Pack<T>;
@@ -85,14 +114,15 @@ __global__ void __launch_bounds__(NT, NT == 256 ? (LN ? TRX_BWD_MINB_LN : TRX_BW
   const int nvec = static_cast<int>(p.C / VEC);
   const float inv_C = __fdiv_rn(1.0f, static_cast<float>(p.C));
 
-  float dwacc[VPT][VEC];
-  float dbacc[LN ? VPT : 1][VEC];
+  constexpr int H2 = VEC / 2;
+  float2 dwacc[VPT][H2];
+  float2 dbacc[LN ? VPT : 1][H2];
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
 #pragma unroll
-    for (int j = 0; j < VEC; ++j) {
-      dwacc[i][j] = 0.0f;
-      if constexpr (LN) dbacc[i][j] = 0.0f;
+    for (int j = 0; j < H2; ++j) {
+      dwacc[i][j] = make_float2(0.0f, 0.0f);
+      if constexpr (LN) dbacc[i][j] = make_float2(0.0f, 0.0f);
     }
 
   for (int64_t row = blockIdx.x; row < p.R; row += gridDim.x) {
@@ -113,45 +143,62 @@ __global__ void __launch_bounds__(NT, NT == 256 ? (LN ? TRX_BWD_MINB_LN : TRX_BW
         const uint32_t row_bytes = static_cast<uint32_t>(nvec) * 16u;
         l2_prefetch_bulk(reinterpret_cast<const T*>(p.x) + prow * p.x_stride, row_bytes);
         l2_prefetch_bulk(reinterpret_cast<const T*>(p.dy) + prow * p.dy_stride, row_bytes);
+        if (p.res) l2_prefetch_bulk(reinterpret_cast<const T*>(p.res) + prow * p.res_stride, row_bytes);
       }
     }
-    float xf[VPT][VEC], gf[VPT][VEC];
+    // fp32 pairs: the arithmetic below is packed (two lanes per instruction)
+    float2 xf[VPT][H2], gf[VPT][H2];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      P::unpack(xr[i], xf[i]);
-      P::unpack(gr[i], gf[i]);
+      P::unpack2(xr[i], xf[i]);
+      P::unpack2(gr[i], gf[i]);
+    }
+    if (p.res) {  // residual forms: the normalised row is the fp32 sum x + r, as in the forward
+      const T* rrow = reinterpret_cast<const T*>(p.res) + row * p.res_stride;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = i * NT + t;
+        if (v < nvec) {
+          float2 rf[H2];
+          P::unpack2(ld_stream16(rrow + static_cast<int64_t>(v) * VEC), rf);
+#pragma unroll
+          for (int j = 0; j < H2; ++j) xf[i][j] = add2(xf[i][j], rf[j]);
+        }
+      }
     }
     // ---- statistics, recomputed from x --------------------------------------------
     float mean = 0.0f, rstd;
     if constexpr (LN) {
-      float s = 0.0f;
+      float2 s2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int i = 0; i < VPT; ++i)
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) s += xf[i][j];
-      mean = block_sum2<NT>(make_float2(s, 0.0f), red, sel).x * inv_C;
-      float cs = 0.0f;
+        for (int j = 0; j < H2; ++j) s2 = add2(s2, xf[i][j]);
+      mean = block_sum2<NT>(make_float2(s2.x + s2.y, 0.0f), red, sel).x * inv_C;
+      const float2 nmean2 = make_float2(-mean, -mean);
+      float2 cs2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         if (i * NT + t < nvec) {  // padding vectors must not contribute (0 - mean)^2
 #pragma unroll
-          for (int j = 0; j < VEC; ++j) {
-            const float d = xf[i][j] - mean;
-            cs = fmaf(d, d, cs);
+          for (int j = 0; j < H2; ++j) {
+            xf[i][j] = add2(xf[i][j], nmean2);  // centred from here on
+            cs2 = fma2(xf[i][j], xf[i][j], cs2);
           }
         }
       }
-      rstd = rsqrtf(fmaf(block_sum2<NT>(make_float2(cs, 0.0f), red, sel).x, inv_C, p.eps));
+      rstd = rsqrtf(fmaf(block_sum2<NT>(make_float2(cs2.x + cs2.y, 0.0f), red, sel).x, inv_C, p.eps));
     } else {
-      float ss = 0.0f;
+      float2 ss2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int i = 0; i < VPT; ++i)
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) ss = fmaf(xf[i][j], xf[i][j], ss);
-      rstd = rsqrtf(fmaf(block_sum2<NT>(make_float2(ss, 0.0f), red, sel).x, inv_C, p.eps));
+        for (int j = 0; j < H2; ++j) ss2 = fma2(xf[i][j], xf[i][j], ss2);
+      rstd = rsqrtf(fmaf(block_sum2<NT>(make_float2(ss2.x + ss2.y, 0.0f), red, sel).x, inv_C, p.eps));
     }
     // ---- n = (x - mean) * rstd, g = dy * w, running column sums, row sums ----------
-    float c1 = 0.0f, c2 = 0.0f;
+    const float2 rstd2 = make_float2(rstd, rstd);
+    float2 c1 = make_float2(0.0f, 0.0f), c2 = make_float2(0.0f, 0.0f);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = i * NT + t;
@@ -159,23 +206,30 @@ __global__ void __launch_bounds__(NT, NT == 256 ? (LN ? TRX_BWD_MINB_LN : TRX_BW
         float wv[VEC];
         if (p.w) load_param_vec<VEC>(p.w, p.w_dtype, static_cast<int64_t>(v) * VEC, wv);
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) {
-          const float n = (xf[i][j] - mean) * rstd;
-          const float dyv = gf[i][j];
-          dwacc[i][j] = fmaf(dyv, n, dwacc[i][j]);
-          if constexpr (LN) dbacc[i][j] += dyv;
-          const float g = p.w ? dyv * wv[j] : dyv;
+        for (int j = 0; j < H2; ++j) {
+          const float2 n = mul2(xf[i][j], rstd2);
+          float2 dyv = gf[i][j];
+          if constexpr (!LN) {
+            if (p.act >= 0) {  // act(RMSNorm): chain through the activation at z = w * n
+              dyv.x *= act_grad<sizeof(T) == 2>(p.act, n.x * wv[2 * j]);
+              dyv.y *= act_grad<sizeof(T) == 2>(p.act, n.y * wv[2 * j + 1]);
+            }
+          }
+          dwacc[i][j] = fma2(dyv, n, dwacc[i][j]);
+          if constexpr (LN) dbacc[i][j] = add2(dbacc[i][j], dyv);
+          const float2 g = p.w ? mul2(dyv, make_float2(wv[2 * j], wv[2 * j + 1])) : dyv;
           xf[i][j] = n;
           gf[i][j] = g;
-          c1 = fmaf(g, n, c1);
-          c2 += g;
+          c1 = fma2(g, n, c1);
+          if constexpr (LN) c2 = add2(c2, g);
         }
       }
     }
-    const float2 c = block_sum2<NT>(make_float2(c1, c2), red, sel);
-    c1 = c.x * inv_C;
-    c2 = LN ? c.y * inv_C : 0.0f;
+    const float2 c = block_sum2<NT>(make_float2(c1.x + c1.y, c2.x + c2.y), red, sel);
+    const float m1 = c.x * inv_C;
+    const float m2 = LN ? c.y * inv_C : 0.0f;
     // ---- dx = rstd * (g - mean(g) - n * mean(g * n)) ------------------------------
+    const float2 nm1 = make_float2(-m1, -m1), nm2 = make_float2(-m2, -m2);
     T* dxrow = reinterpret_cast<T*>(p.dx) + row * p.dx_stride;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -183,7 +237,13 @@ __global__ void __launch_bounds__(NT, NT == 256 ? (LN ? TRX_BWD_MINB_LN : TRX_BW
       if (v < nvec) {
         float o[VEC];
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) o[j] = rstd * (gf[i][j] - c2 - xf[i][j] * c1);
+        for (int j = 0; j < H2; ++j) {
+          float2 d = fma2(xf[i][j], nm1, gf[i][j]);
+          if constexpr (LN) d = add2(d, nm2);
+          d = mul2(d, rstd2);
+          o[2 * j] = d.x;
+          o[2 * j + 1] = d.y;
+        }
         st_stream16(dxrow + static_cast<int64_t>(v) * VEC, P::pack(o));
       }
     }
@@ -198,11 +258,11 @@ __global__ void __launch_bounds__(NT, NT == 256 ? (LN ? TRX_BWD_MINB_LN : TRX_BW
       for (int q = 0; q < VEC / 4; ++q) {
         if (p.dw_part)
           *reinterpret_cast<float4*>(p.dw_part + off + 4 * q) =
-              make_float4(dwacc[i][4 * q], dwacc[i][4 * q + 1], dwacc[i][4 * q + 2], dwacc[i][4 * q + 3]);
+              make_float4(dwacc[i][2 * q].x, dwacc[i][2 * q].y, dwacc[i][2 * q + 1].x, dwacc[i][2 * q + 1].y);
         if constexpr (LN) {
           if (p.db_part)
             *reinterpret_cast<float4*>(p.db_part + off + 4 * q) =
-                make_float4(dbacc[i][4 * q], dbacc[i][4 * q + 1], dbacc[i][4 * q + 2], dbacc[i][4 * q + 3]);
+                make_float4(dbacc[i][2 * q].x, dbacc[i][2 * q].y, dbacc[i][2 * q + 1].x, dbacc[i][2 * q + 1].y);
         }
       }
     }
@@ -220,23 +280,32 @@ __global__ void __launch_bounds__(256) norm_bwd_generic_dx(const NormBwdParams p
     const T* xrow = reinterpret_cast<const T*>(p.x) + row * p.x_stride;
     const T* grow = reinterpret_cast<const T*>(p.dy) + row * p.dy_stride;
     T* dxrow = reinterpret_cast<T*>(p.dx) + row * p.dx_stride;
+    const T* rrow = p.res ? reinterpret_cast<const T*>(p.res) + row * p.res_stride : nullptr;
+    auto xval = [&](int64_t c) -> float {  // x, or the fp32 sum x + residual
+      const float f = P::load1(xrow + c);
+      return rrow ? f + P::load1(rrow + c) : f;
+    };
     float mean = 0.0f;
     if constexpr (LN) {
       float s = 0.0f;
-      for (int64_t c = threadIdx.x; c < p.C; c += 256) s += P::load1(xrow + c);
+      for (int64_t c = threadIdx.x; c < p.C; c += 256) s += xval(c);
       mean = block_sum2(make_float2(s, 0.0f), red, sel).x * inv_C;
     }
     float cs = 0.0f;
     for (int64_t c = threadIdx.x; c < p.C; c += 256) {
-      const float d = P::load1(xrow + c) - mean;
+      const float d = xval(c) - mean;
       cs = fmaf(d, d, cs);
     }
     const float rstd = rsqrtf(fmaf(block_sum2(make_float2(cs, 0.0f), red, sel).x, inv_C, p.eps));
     float c1 = 0.0f, c2 = 0.0f;
     for (int64_t c = threadIdx.x; c < p.C; c += 256) {
-      const float n = (P::load1(xrow + c) - mean) * rstd;
+      const float n = (xval(c) - mean) * rstd;
       float g = P::load1(grow + c);
-      if (p.w) g *= load_param1(p.w, p.w_dtype, c);
+      if (p.w) {
+        const float wc = load_param1(p.w, p.w_dtype, c);
+        if (p.act >= 0) g *= act_grad<sizeof(T) == 2>(p.act, n * wc);
+        g *= wc;
+      }
       c1 = fmaf(g, n, c1);
       c2 += g;
     }
@@ -244,9 +313,13 @@ __global__ void __launch_bounds__(256) norm_bwd_generic_dx(const NormBwdParams p
     c1 = cc.x * inv_C;
     c2 = LN ? cc.y * inv_C : 0.0f;
     for (int64_t c = threadIdx.x; c < p.C; c += 256) {
-      const float n = (P::load1(xrow + c) - mean) * rstd;
+      const float n = (xval(c) - mean) * rstd;
       float g = P::load1(grow + c);
-      if (p.w) g *= load_param1(p.w, p.w_dtype, c);
+      if (p.w) {
+        const float wc = load_param1(p.w, p.w_dtype, c);
+        if (p.act >= 0) g *= act_grad<sizeof(T) == 2>(p.act, n * wc);
+        g *= wc;
+      }
       P::store1(dxrow + c, rstd * (g - c2 - n * c1));
     }
     if (threadIdx.x == 0 && p.stats) {
@@ -265,8 +338,12 @@ __global__ void __launch_bounds__(256) norm_bwd_generic_partials(const NormBwdPa
   float dw = 0.0f, db = 0.0f;
   for (int64_t row = blockIdx.y; row < p.R; row += gridDim.y) {
     const float dyv = P::load1(reinterpret_cast<const T*>(p.dy) + row * p.dy_stride + c);
-    const float xv = P::load1(reinterpret_cast<const T*>(p.x) + row * p.x_stride + c);
-    dw = fmaf(dyv, (xv - p.stats[2 * row]) * p.stats[2 * row + 1], dw);
+    float xv = P::load1(reinterpret_cast<const T*>(p.x) + row * p.x_stride + c);
+    if (p.res) xv += P::load1(reinterpret_cast<const T*>(p.res) + row * p.res_stride + c);
+    const float n = (xv - p.stats[2 * row]) * p.stats[2 * row + 1];
+    float dz = dyv;
+    if (p.act >= 0) dz *= act_grad<sizeof(T) == 2>(p.act, n * load_param1(p.w, p.w_dtype, c));
+    dw = fmaf(dz, n, dw);
     db += dyv;
   }
   const int64_t off = static_cast<int64_t>(blockIdx.y) * p.C + c;
@@ -274,21 +351,35 @@ __global__ void __launch_bounds__(256) norm_bwd_generic_partials(const NormBwdPa
   if (p.db_part) p.db_part[off] = db;
 }
 
-// out[c] = sum over the P rows of part (fixed order), stored in the parameter dtype.
-__global__ void __launch_bounds__(256) reduce_partials_kernel(const float* part, int P_rows,
-                                                              int64_t C, void* out, int dtype) {
-  __shared__ float sm[8][33];
+// out[c] = sum over the P rows of part (fixed order), stored in the parameter dtype. 32 columns x
+// 32 row slices per CTA: a warp reads 128 contiguous bytes, a thread adds every 32nd row, the 32
+// slice sums of a column are added in slice order. blockIdx.y selects dW (0) or db (1).
+struct ReduceParams {
+  const float* part[2];
+  void* out[2];
+};
+__global__ void __launch_bounds__(1024) reduce_partials_kernel(const ReduceParams rp, int P_rows,
+                                                               int64_t C, int dtype) {
+  __shared__ float sm[32][33];
+  const float* part = rp.part[blockIdx.y];
+  void* out = rp.out[blockIdx.y];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int64_t c = static_cast<int64_t>(blockIdx.x) * 32 + tx;
-  float acc = 0.0f;
-  if (c < C)
-    for (int pr = ty; pr < P_rows; pr += 8) acc += part[static_cast<int64_t>(pr) * C + c];
-  sm[ty][tx] = acc;
+  float a0 = 0.0f, a1 = 0.0f;
+  if (c < C) {
+    int pr = ty;
+    for (; pr + 32 < P_rows; pr += 64) {  // two loads in flight per thread
+      a0 += part[static_cast<int64_t>(pr) * C + c];
+      a1 += part[static_cast<int64_t>(pr + 32) * C + c];
+    }
+    if (pr < P_rows) a0 += part[static_cast<int64_t>(pr) * C + c];
+  }
+  sm[ty][tx] = a0 + a1;
   __syncthreads();
   if (ty == 0 && c < C) {
     float s = sm[0][tx];
 #pragma unroll
-    for (int i = 1; i < 8; ++i) s += sm[i][tx];
+    for (int i = 1; i < 32; ++i) s += sm[i][tx];
     if (dtype == TRX_F32) reinterpret_cast<float*>(out)[c] = s;
     else if (dtype == TRX_BF16) reinterpret_cast<__nv_bfloat16*>(out)[c] = __float2bfloat16_rn(s);
     else reinterpret_cast<__half*>(out)[c] = __float2half_rn(s);
@@ -337,6 +428,7 @@ static int launch_norm_bwd(NormBwdParams p, void* dw, void* db, float* ws, cudaS
                   aligned_to(p.dx, 16) && (p.x_stride % VEC == 0) && (p.dy_stride % VEC == 0) &&
                   (p.dx_stride % VEC == 0) && aligned_to(ws, 16);
     if (p.w) vec_ok = vec_ok && aligned_to(p.w, 16);
+    if (p.res) vec_ok = vec_ok && aligned_to(p.res, 16) && (p.res_stride % VEC == 0);
     const int64_t nvec = p.C / VEC;
     if (vec_ok && nvec <= 1024) {
       // few vectors per thread: the running column sums cost 8 (16 for LayerNorm) registers each
@@ -354,9 +446,14 @@ static int launch_norm_bwd(NormBwdParams p, void* dw, void* db, float* ws, cudaS
   } else {
     P_rows = 0;
   }
-  const unsigned cgrid = static_cast<unsigned>((p.C + 31) / 32);
-  if (dw) reduce_partials_kernel<<<cgrid, 256, 0, stream>>>(p.dw_part, static_cast<int>(P_rows), p.C, dw, p.w_dtype);
-  if (db) reduce_partials_kernel<<<cgrid, 256, 0, stream>>>(p.db_part, static_cast<int>(P_rows), p.C, db, p.w_dtype);
+  if (dw || db) {
+    ReduceParams rp{};
+    int n = 0;
+    if (dw) { rp.part[n] = p.dw_part; rp.out[n] = dw; ++n; }
+    if (db) { rp.part[n] = p.db_part; rp.out[n] = db; ++n; }
+    const dim3 cgrid(static_cast<unsigned>((p.C + 31) / 32), static_cast<unsigned>(n));
+    reduce_partials_kernel<<<cgrid, 1024, 0, stream>>>(rp, static_cast<int>(P_rows), p.C, p.w_dtype);
+  }
   return cudaGetLastError() == cudaSuccess ? TRX_OK : TRX_ERR_CUDA;
 }
 
@@ -372,19 +469,21 @@ template <bool LN>
 static int norm_bwd_entry(const void* dy, const void* x, const void* w, void* dx, void* dw, void* db,
                           int64_t R, int64_t C, int64_t dy_stride, int64_t x_stride,
                           int64_t dx_stride, float eps, int x_dtype, int w_dtype, void* workspace,
-                          size_t workspace_bytes, void* stream) {
+                          size_t workspace_bytes, void* stream, const void* res = nullptr,
+                          int64_t res_stride = 0, int act = -1) {
   if (!bwd_dtype_ok(x_dtype) || !bwd_dtype_ok(w_dtype)) return TRX_ERR_DTYPE;
   if (R < 0 || C <= 0) return TRX_ERR_SHAPE;
   if (R > 0 && (!dy || !x || !dx)) return TRX_ERR_NULL_POINTER;
   if (!LN && !w) return TRX_ERR_NULL_POINTER;
   if (R > 0 && (dy_stride < C || x_stride < C || dx_stride < C)) return TRX_ERR_STRIDE;
+  if (R > 0 && res && res_stride < C) return TRX_ERR_STRIDE;
   if (R == 0 && !dw && !db) return TRX_OK;
   if (!workspace || workspace_bytes < norm_bwd_workspace(R, C)) return TRX_ERR_WORKSPACE;
   if (!aligned_to(workspace, 4)) return TRX_ERR_ALIGNMENT;
   NormBwdParams p{};
-  p.dy = dy; p.x = x; p.w = w; p.dx = dx;
+  p.dy = dy; p.x = x; p.w = w; p.dx = dx; p.res = res; p.res_stride = res_stride;
   p.R = R; p.C = C; p.dy_stride = dy_stride; p.x_stride = x_stride; p.dx_stride = dx_stride;
-  p.eps = eps; p.w_dtype = w_dtype;
+  p.eps = eps; p.w_dtype = w_dtype; p.act = act;
   float* ws = static_cast<float*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (x_dtype) {
@@ -535,6 +634,43 @@ extern "C" int trx_layernorm_bwd(const void* dy, const void* x, const void* w_or
   return norm_bwd_entry<true>(dy, x, w_or_null, dx, dw_or_null, db_or_null, R, C, dy_row_stride,
                               x_row_stride, dx_row_stride, eps, x_dtype, wb_dtype, workspace,
                               workspace_bytes, stream);
+}
+
+extern "C" int trx_residual_rmsnorm_bwd(const void* dy, const void* x, const void* residual,
+                                        const void* w, void* dx, void* dw_or_null, int64_t R,
+                                        int64_t C, int64_t dy_row_stride, int64_t x_row_stride,
+                                        int64_t res_row_stride, int64_t dx_row_stride, float eps,
+                                        int x_dtype, int w_dtype, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+  if (R > 0 && !residual) return TRX_ERR_NULL_POINTER;
+  return norm_bwd_entry<false>(dy, x, w, dx, dw_or_null, nullptr, R, C, dy_row_stride, x_row_stride,
+                               dx_row_stride, eps, x_dtype, w_dtype, workspace, workspace_bytes,
+                               stream, residual, res_row_stride);
+}
+
+extern "C" int trx_residual_layernorm_bwd(const void* dy, const void* x, const void* residual,
+                                          const void* w_or_null, void* dx, void* dw_or_null,
+                                          void* db_or_null, int64_t R, int64_t C,
+                                          int64_t dy_row_stride, int64_t x_row_stride,
+                                          int64_t res_row_stride, int64_t dx_row_stride, float eps,
+                                          int x_dtype, int wb_dtype, void* workspace,
+                                          size_t workspace_bytes, void* stream) {
+  if (R > 0 && !residual) return TRX_ERR_NULL_POINTER;
+  return norm_bwd_entry<true>(dy, x, w_or_null, dx, dw_or_null, db_or_null, R, C, dy_row_stride,
+                              x_row_stride, dx_row_stride, eps, x_dtype, wb_dtype, workspace,
+                              workspace_bytes, stream, residual, res_row_stride);
+}
+
+extern "C" int trx_rmsnorm_act_bwd(const void* dy, const void* x, const void* w, void* dx,
+                                   void* dw_or_null, int64_t R, int64_t C, int64_t dy_row_stride,
+                                   int64_t x_row_stride, int64_t dx_row_stride, float eps, int act,
+                                   int x_dtype, int w_dtype, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+  if (act != TRX_ACT_MISH && act != TRX_ACT_QUICKGELU && act != TRX_ACT_SQUARED_RELU)
+    return TRX_ERR_UNSUPPORTED;
+  return norm_bwd_entry<false>(dy, x, w, dx, dw_or_null, nullptr, R, C, dy_row_stride, x_row_stride,
+                               dx_row_stride, eps, x_dtype, w_dtype, workspace, workspace_bytes,
+                               stream, nullptr, 0, act);
 }
 
 extern "C" int trx_glu_bwd(const void* dy, const void* up, const void* gate, void* dup, void* dgate,

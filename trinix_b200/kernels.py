@@ -6,12 +6,12 @@ object with the same two static methods is a drop-in. Here `apply` runs the sm_1
 kernel through the C ABI. The classes keep the reference's `Triton*` names because that
 is the interface being replaced; nothing in this package uses Triton.
 
-RMSNorm, LayerNorm, RoPE and the GLUs are differentiable: their autograd functions run the
-backward kernels of the same library (the reference's Triton*Function.backward methods,
-e.g. trinix/kernels/rmsnorm_kernel.py:270-321). Attention, the fused forms and the int8 ops are
-forward only, as attention is in the reference (TritonAttentionKernel has no backward): their
-outputs are attached to the autograd graph so that a later `.backward()` fails with a clear
-error instead of silently producing no gradient.
+RMSNorm, LayerNorm, their residual and activation forms, RoPE and the GLUs are differentiable:
+their autograd functions run the backward kernels of the same library (the reference's
+Triton*Function.backward methods, e.g. trinix/kernels/rmsnorm_kernel.py:270-321). Attention and
+the int8 ops are forward only, as attention is in the reference (TritonAttentionKernel has no
+backward): their outputs are attached to the autograd graph so that a later `.backward()` fails
+with a clear error instead of silently producing no gradient.
 """
 from __future__ import annotations
 
@@ -91,6 +91,65 @@ class _LayerNormFn(torch.autograd.Function):
         return dx, dw, db, None
 
 
+class _ResidualRMSNormFn(torch.autograd.Function):
+    """Counterpart of TritonFusedResidualRMSNormFunction
+    (trinix/kernels/fused/residual_rmsnorm_kernel.py:209-303): x and the residual share one
+    gradient, the RMSNorm gradient at the fp32 sum."""
+
+    @staticmethod
+    def forward(ctx, X, Residual, W, eps):
+        ctx.save_for_backward(X, Residual, W)
+        ctx.eps = eps
+        return ops.residual_rmsnorm(X, Residual, W, eps)
+
+    @staticmethod
+    def backward(ctx, dY):
+        X, Residual, W = ctx.saved_tensors
+        dx, dw = ops.rmsnorm_backward(dY, X, W, ctx.eps, need_dw=ctx.needs_input_grad[2],
+                                      residual=Residual)
+        return dx, dx, dw, None
+
+
+class _ResidualLayerNormFn(torch.autograd.Function):
+    """Counterpart of TritonFusedResidualLayerNormFunction
+    (trinix/kernels/fused/residual_layernorm_kernel.py:228-335)."""
+
+    @staticmethod
+    def forward(ctx, X, Residual, W, b, eps):
+        ctx.save_for_backward(X, Residual, W)
+        ctx.eps = eps
+        ctx.bias_dtype = b.dtype if b is not None else None
+        return ops.residual_layernorm(X, Residual, W, b, eps)
+
+    @staticmethod
+    def backward(ctx, dY):
+        X, Residual, W = ctx.saved_tensors
+        need_db = ctx.bias_dtype is not None and ctx.needs_input_grad[3]
+        dx, dw, db = ops.layernorm_backward(dY, X, W, ctx.eps, need_dw=ctx.needs_input_grad[2],
+                                            need_db=need_db, residual=Residual)
+        if db is not None and db.dtype != ctx.bias_dtype:
+            db = db.to(ctx.bias_dtype)
+        return dx, dx, dw, db, None
+
+
+class _RMSNormActivationFn(torch.autograd.Function):
+    """Counterpart of TritonFusedRMSNormActivationFunction
+    (trinix/kernels/fused/rmsnorm_activation_kernel.py:236-330)."""
+
+    @staticmethod
+    def forward(ctx, X, W, eps, activation):
+        ctx.save_for_backward(X, W)
+        ctx.eps, ctx.activation = eps, activation
+        return ops.rmsnorm_activation(X, W, eps, activation)
+
+    @staticmethod
+    def backward(ctx, dY):
+        X, W = ctx.saved_tensors
+        dx, dw = ops.rmsnorm_backward(dY, X, W, ctx.eps, need_dw=ctx.needs_input_grad[1],
+                                      activation=ctx.activation)
+        return dx, dw, None, None
+
+
 class _GLUFn(torch.autograd.Function):
     """Counterpart of Triton{SwiGLU,GeGLU,ReGLU}Function (e.g.
     trinix/kernels/swigelu_kernel.py:94-180): saves the input, one backward kernel."""
@@ -162,7 +221,9 @@ class TritonFusedResidualRMSNormKernel:
 
     @staticmethod
     def apply(X: torch.Tensor, Residual: torch.Tensor, W: torch.Tensor, eps: float) -> torch.Tensor:
-        return _run(lambda x, r, w: ops.residual_rmsnorm(x, r, w, eps), X, Residual, W)
+        if _needs_graph(X, Residual, W):
+            return _ResidualRMSNormFn.apply(X, Residual, W, eps)
+        return ops.residual_rmsnorm(X, Residual, W, eps)
 
 
 class TritonFusedResidualLayerNormKernel:
@@ -176,7 +237,9 @@ class TritonFusedResidualLayerNormKernel:
     @staticmethod
     def apply(X: torch.Tensor, Residual: torch.Tensor, W: Optional[torch.Tensor],
               b: Optional[torch.Tensor], eps: float) -> torch.Tensor:
-        return _run(lambda x, r, w, bb: ops.residual_layernorm(x, r, w, bb, eps), X, Residual, W, b)
+        if _needs_graph(X, Residual, W, b):
+            return _ResidualLayerNormFn.apply(X, Residual, W, b, eps)
+        return ops.residual_layernorm(X, Residual, W, b, eps)
 
 
 class TritonFusedRMSNormActivationKernel:
@@ -189,7 +252,9 @@ class TritonFusedRMSNormActivationKernel:
 
     @staticmethod
     def apply(X: torch.Tensor, W: torch.Tensor, eps: float, activation: str = "mish") -> torch.Tensor:
-        return _run(lambda x, w: ops.rmsnorm_activation(x, w, eps, activation), X, W)
+        if _needs_graph(X, W):
+            return _RMSNormActivationFn.apply(X, W, eps, activation)
+        return ops.rmsnorm_activation(X, W, eps, activation)
 
 
 class TritonRoPEKernel:

@@ -384,12 +384,22 @@ def _norm_bwd_workspace(rows: int, cols: int, dev: torch.device) -> torch.Tensor
 
 
 def rmsnorm_backward(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
-                     need_dw: bool = True):
+                     need_dw: bool = True, residual: Optional[torch.Tensor] = None,
+                     activation: Optional[str] = None):
     """(dx, dw) of rmsnorm(x, weight, eps) given dy; dw is None when need_dw is False. The row
-    statistics are recomputed from x; dw is summed in fp32 in a fixed order."""
-    dev = _need_cuda(dy, x, weight)
+    statistics are recomputed from x; dw is summed in fp32 in a fixed order. With `residual`, the
+    gradient of residual_rmsnorm(x, residual, ...): dx is then also the residual's gradient. With
+    `activation`, the gradient of rmsnorm_activation(x, weight, eps, activation)."""
+    if activation is not None and activation not in ROW_ACTIVATIONS:
+        raise ValueError(f"Unsupported activation '{activation}'. "
+                         f"Supported: {sorted(ROW_ACTIVATIONS)}")
+    if activation is not None and residual is not None:
+        raise ValueError("residual and activation cannot be combined")
+    dev = _need_cuda(dy, x, weight, residual)
     if dy.shape != x.shape or dy.dtype != x.dtype:
         raise ValueError("dy must have the shape and dtype of x")
+    if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype):
+        raise ValueError("residual must have the shape and dtype of x")
     if weight.numel() != x.shape[-1]:
         raise ValueError(f"weight has {weight.numel()} elements, rows have {x.shape[-1]}")
     x2, dy2 = _rows(x), _rows(dy)
@@ -397,23 +407,44 @@ def rmsnorm_backward(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, ep
     dx = torch.empty((x2.shape[0], x2.shape[1]), dtype=x.dtype, device=dev)
     dw = torch.empty(x2.shape[1], dtype=w.dtype, device=dev) if need_dw else None
     ws = _norm_bwd_workspace(x2.shape[0], x2.shape[1], dev)
+    lib = _lib.load()
     with torch.cuda.device(dev):
-        rc = _lib.load().trx_rmsnorm_bwd(
-            _ptr(dy2), _ptr(x2), _ptr(w), _ptr(dx), _ptr(dw), x2.shape[0], x2.shape[1],
-            _row_stride(dy2), _row_stride(x2), x2.shape[1], float(eps), _code(x2), _code(w),
-            _ptr(ws), ws.numel(), _stream(dev))
-    _lib.check("trx_rmsnorm_bwd", rc)
+        if activation is not None:
+            name = "trx_rmsnorm_act_bwd"
+            rc = lib.trx_rmsnorm_act_bwd(
+                _ptr(dy2), _ptr(x2), _ptr(w), _ptr(dx), _ptr(dw), x2.shape[0], x2.shape[1],
+                _row_stride(dy2), _row_stride(x2), x2.shape[1], float(eps),
+                ROW_ACTIVATIONS[activation], _code(x2), _code(w), _ptr(ws), ws.numel(),
+                _stream(dev))
+        elif residual is None:
+            name = "trx_rmsnorm_bwd"
+            rc = lib.trx_rmsnorm_bwd(
+                _ptr(dy2), _ptr(x2), _ptr(w), _ptr(dx), _ptr(dw), x2.shape[0], x2.shape[1],
+                _row_stride(dy2), _row_stride(x2), x2.shape[1], float(eps), _code(x2), _code(w),
+                _ptr(ws), ws.numel(), _stream(dev))
+        else:
+            name = "trx_residual_rmsnorm_bwd"
+            r2 = _rows(residual)
+            rc = lib.trx_residual_rmsnorm_bwd(
+                _ptr(dy2), _ptr(x2), _ptr(r2), _ptr(w), _ptr(dx), _ptr(dw), x2.shape[0],
+                x2.shape[1], _row_stride(dy2), _row_stride(x2), _row_stride(r2), x2.shape[1],
+                float(eps), _code(x2), _code(w), _ptr(ws), ws.numel(), _stream(dev))
+    _lib.check(name, rc)
     _count()
     return dx.view(x.shape), (dw.view(weight.shape) if need_dw else None)
 
 
 def layernorm_backward(dy: torch.Tensor, x: torch.Tensor, weight: Optional[torch.Tensor],
-                       eps: float = 1e-5, need_dw: bool = True, need_db: bool = True):
+                       eps: float = 1e-5, need_dw: bool = True, need_db: bool = True,
+                       residual: Optional[torch.Tensor] = None):
     """(dx, dw, db) of layernorm(x, weight, bias, eps) given dy; weight may be None (then dw is
-    None); db is returned in the weight's dtype (x's dtype without a weight)."""
-    dev = _need_cuda(dy, x, weight)
+    None); db is returned in the weight's dtype (x's dtype without a weight). With `residual`,
+    the gradient of residual_layernorm(x, residual, ...): dx is then also the residual's."""
+    dev = _need_cuda(dy, x, weight, residual)
     if dy.shape != x.shape or dy.dtype != x.dtype:
         raise ValueError("dy must have the shape and dtype of x")
+    if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype):
+        raise ValueError("residual must have the shape and dtype of x")
     if weight is not None and weight.numel() != x.shape[-1]:
         raise ValueError("weight size does not match the normalised dim")
     x2, dy2 = _rows(x), _rows(dy)
@@ -424,12 +455,22 @@ def layernorm_backward(dy: torch.Tensor, x: torch.Tensor, weight: Optional[torch
     dw = torch.empty(x2.shape[1], dtype=p_dtype, device=dev) if need_dw else None
     db = torch.empty(x2.shape[1], dtype=p_dtype, device=dev) if need_db else None
     ws = _norm_bwd_workspace(x2.shape[0], x2.shape[1], dev)
+    lib = _lib.load()
     with torch.cuda.device(dev):
-        rc = _lib.load().trx_layernorm_bwd(
-            _ptr(dy2), _ptr(x2), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db), x2.shape[0], x2.shape[1],
-            _row_stride(dy2), _row_stride(x2), x2.shape[1], float(eps), _code(x2),
-            _DTYPE_CODE[p_dtype], _ptr(ws), ws.numel(), _stream(dev))
-    _lib.check("trx_layernorm_bwd", rc)
+        if residual is None:
+            name = "trx_layernorm_bwd"
+            rc = lib.trx_layernorm_bwd(
+                _ptr(dy2), _ptr(x2), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db), x2.shape[0],
+                x2.shape[1], _row_stride(dy2), _row_stride(x2), x2.shape[1], float(eps), _code(x2),
+                _DTYPE_CODE[p_dtype], _ptr(ws), ws.numel(), _stream(dev))
+        else:
+            name = "trx_residual_layernorm_bwd"
+            r2 = _rows(residual)
+            rc = lib.trx_residual_layernorm_bwd(
+                _ptr(dy2), _ptr(x2), _ptr(r2), _ptr(w), _ptr(dx), _ptr(dw), _ptr(db), x2.shape[0],
+                x2.shape[1], _row_stride(dy2), _row_stride(x2), _row_stride(r2), x2.shape[1],
+                float(eps), _code(x2), _DTYPE_CODE[p_dtype], _ptr(ws), ws.numel(), _stream(dev))
+    _lib.check(name, rc)
     _count()
     return dx.view(x.shape), dw, db
 
