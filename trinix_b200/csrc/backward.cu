@@ -77,6 +77,20 @@ __device__ __forceinline__ float2 block_sum2(float2 v, float2 (*red)[NT / 32], i
   return r;
 }
 
+// Sum of one float over the NT threads of a CTA, through the x lanes of the same banks.
+template <int NT = 256>
+__device__ __forceinline__ float block_sum1(float v, float2 (*red)[NT / 32], int& sel) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) red[sel][threadIdx.x >> 5].x = v;
+  __syncthreads();
+  float r = red[sel][0].x;
+#pragma unroll
+  for (int i = 1; i < NT / 32; ++i) r += red[sel][i].x;
+  sel ^= 1;
+  return r;
+}
+
 // act'(z) for the activations of act(RMSNorm(x)): mish z tanh(softplus z), quickgelu
 // z sigmoid(1.702 z), squared ReLU max(z, 0)^2. With q = e^z (e^z + 2): tanh(softplus z) =
 // q / (q + 2) and 1 - tanh = 2 / (q + 2), so 1 - tanh^2 carries no cancellation; z is clamped at
@@ -174,7 +188,7 @@ __global__ void __launch_bounds__(NT, NT == 256 ? (LN ? TRX_BWD_MINB_LN : TRX_BW
       for (int i = 0; i < VPT; ++i)
 #pragma unroll
         for (int j = 0; j < H2; ++j) s2 = add2(s2, xf[i][j]);
-      mean = block_sum2<NT>(make_float2(s2.x + s2.y, 0.0f), red, sel).x * inv_C;
+      mean = block_sum1<NT>(s2.x + s2.y, red, sel) * inv_C;
       const float2 nmean2 = make_float2(-mean, -mean);
       float2 cs2 = make_float2(0.0f, 0.0f);
 #pragma unroll
@@ -187,14 +201,14 @@ __global__ void __launch_bounds__(NT, NT == 256 ? (LN ? TRX_BWD_MINB_LN : TRX_BW
           }
         }
       }
-      rstd = rsqrtf(fmaf(block_sum2<NT>(make_float2(cs2.x + cs2.y, 0.0f), red, sel).x, inv_C, p.eps));
+      rstd = rsqrtf(fmaf(block_sum1<NT>(cs2.x + cs2.y, red, sel), inv_C, p.eps));
     } else {
       float2 ss2 = make_float2(0.0f, 0.0f);
 #pragma unroll
       for (int i = 0; i < VPT; ++i)
 #pragma unroll
         for (int j = 0; j < H2; ++j) ss2 = fma2(xf[i][j], xf[i][j], ss2);
-      rstd = rsqrtf(fmaf(block_sum2<NT>(make_float2(ss2.x + ss2.y, 0.0f), red, sel).x, inv_C, p.eps));
+      rstd = rsqrtf(fmaf(block_sum1<NT>(ss2.x + ss2.y, red, sel), inv_C, p.eps));
     }
     // ---- n = (x - mean) * rstd, g = dy * w, running column sums, row sums ----------
     const float2 rstd2 = make_float2(rstd, rstd);
@@ -225,9 +239,14 @@ __global__ void __launch_bounds__(NT, NT == 256 ? (LN ? TRX_BWD_MINB_LN : TRX_BW
         }
       }
     }
-    const float2 c = block_sum2<NT>(make_float2(c1.x + c1.y, c2.x + c2.y), red, sel);
-    const float m1 = c.x * inv_C;
-    const float m2 = LN ? c.y * inv_C : 0.0f;
+    float m1, m2 = 0.0f;
+    if constexpr (LN) {
+      const float2 c = block_sum2<NT>(make_float2(c1.x + c1.y, c2.x + c2.y), red, sel);
+      m1 = c.x * inv_C;
+      m2 = c.y * inv_C;
+    } else {
+      m1 = block_sum1<NT>(c1.x + c1.y, red, sel) * inv_C;
+    }
     // ---- dx = rstd * (g - mean(g) - n * mean(g * n)) ------------------------------
     const float2 nm1 = make_float2(-m1, -m1), nm2 = make_float2(-m2, -m2);
     T* dxrow = reinterpret_cast<T*>(p.dx) + row * p.dx_stride;
