@@ -295,6 +295,21 @@ def test_mirror_modules_train_through_the_kernels(cuda):
         assert rel_err(xl.grad.cpu(), xr.grad) <= (2e-4 if cls is T.FastGeGLU else 2e-5)
 
 
+def test_broadcast_gradients_are_materialised(cuda):
+    """y.sum().backward() hands the backward a gradient expanded from one scalar (all strides 0)."""
+    x = torch.randn(6, 4104, device=cuda, requires_grad=True)
+    w = torch.ones(4104, device=cuda, requires_grad=True)
+    T.TritonRMSNormKernel.apply(x, w, 1e-6).sum().backward()
+    xr, wr = x.detach().cpu().requires_grad_(True), w.detach().cpu().requires_grad_(True)
+    R.rmsnorm_ref(xr, wr, 1e-6).sum().backward()
+    assert rel_err(x.grad.cpu(), xr.grad) <= 1e-4 and rel_err(w.grad.cpu(), wr.grad) <= 1e-4
+    xg = torch.randn(5, 2 * 640, device=cuda, requires_grad=True)
+    T.TritonSwiGLUKernel.apply(xg).sum().backward()
+    xgr = xg.detach().cpu().requires_grad_(True)
+    R.swiglu_ref(xgr).sum().backward()
+    assert rel_err(xg.grad.cpu(), xgr.grad) <= 2e-5
+
+
 def test_forward_only_ops_still_refuse_backward(cuda):
     q = torch.randn(1, 128, 2, 128, device=cuda, dtype=torch.bfloat16, requires_grad=True)
     out = T.TritonAttentionKernel.apply(q, q, q, causal=True)

@@ -62,7 +62,8 @@ def _rows(x: torch.Tensor) -> torch.Tensor:
     """View (or, if unavoidable, copy) x as 2-D (rows, C) with a unit column stride."""
     c = x.shape[-1]
     x2 = x.reshape(-1, c)
-    if x2.numel() and x2.stride(-1) != 1:
+    # expanded tensors (a broadcast gradient, say) have rows that overlap: materialise them
+    if x2.numel() and (x2.stride(-1) != 1 or (x2.shape[0] > 1 and x2.stride(0) < c)):
         x2 = x2.contiguous()
     return x2
 
