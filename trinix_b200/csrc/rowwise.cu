@@ -34,6 +34,13 @@ namespace trx {
 #define TRX_ROW_L2_PREFETCH 1
 #endif
 
+// Sum of squares of a 16-bit row straight from the packed words with the mixed-precision FMA
+// (fp32 accumulator, 16-bit multiplicands: the product of two 16-bit values is exact in fp32, so
+// the result equals the fp32 FMA on unpacked values bit for bit) instead of unpack + packed FMA.
+#ifndef TRX_ROW_MIXED_SS
+#define TRX_ROW_MIXED_SS 1
+#endif
+
 enum RowOp {
   OP_RMSNORM = 0,
   OP_LAYERNORM = 1,
@@ -173,6 +180,22 @@ __device__ __forceinline__ float rsqrt_approx(float v) {
   return r;
 }
 
+// acc_lo += lo(u)^2, acc_hi += hi(u)^2 for a word of two 16-bit values, in fp32.
+template <typename T>
+__device__ __forceinline__ void sq_acc_word(uint32_t u, float& acc_lo, float& acc_hi) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    asm("{.reg .b16 l, h; mov.b32 {l, h}, %2; fma.rn.f32.bf16 %0, l, l, %0; "
+        "fma.rn.f32.bf16 %1, h, h, %1;}"
+        : "+f"(acc_lo), "+f"(acc_hi)
+        : "r"(u));
+  } else {
+    asm("{.reg .b16 l, h; mov.b32 {l, h}, %2; fma.rn.f32.f16 %0, l, l, %0; "
+        "fma.rn.f32.f16 %1, h, h, %1;}"
+        : "+f"(acc_lo), "+f"(acc_hi)
+        : "r"(u));
+  }
+}
+
 // FULL: every row has exactly TPR * VPT vectors and the row count is a multiple of the rows per
 // CTA, so no vector of any thread is padding. The guards disappear, and with them some thirty
 // branches per warp and row that kept the four vectors of a thread from being scheduled together.
@@ -266,16 +289,27 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
     // ---- 2. statistics -------------------------------------------------------------
     if constexpr (op_is_rms(OP)) {
       float2 ss2 = make_float2(0.0f, 0.0f), ss2b = make_float2(0.0f, 0.0f);  // two chains
+      if constexpr (TRX_ROW_MIXED_SS && VEC == 8 && !HAS_RES) {
+        // same four accumulation chains, same order, as the unpacked form below
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        float2 f2[VEC / 2];
-        P::unpack2(raw[i], f2);
-        add_residual(i, f2);
+        for (int i = 0; i < VPT; ++i) {
+          sq_acc_word<T>(raw[i].x, ss2.x, ss2.y);
+          sq_acc_word<T>(raw[i].y, ss2b.x, ss2b.y);
+          sq_acc_word<T>(raw[i].z, ss2.x, ss2.y);
+          sq_acc_word<T>(raw[i].w, ss2b.x, ss2b.y);
+        }
+      } else {
 #pragma unroll
-        for (int j = 0; j < VEC / 2; ++j) {
-          if (j & 1) ss2b = fma2(f2[j], f2[j], ss2b);
-          else ss2 = fma2(f2[j], f2[j], ss2);
-          if constexpr (KEEP_F32) xf[i][j] = f2[j];
+        for (int i = 0; i < VPT; ++i) {
+          float2 f2[VEC / 2];
+          P::unpack2(raw[i], f2);
+          add_residual(i, f2);
+#pragma unroll
+          for (int j = 0; j < VEC / 2; ++j) {
+            if (j & 1) ss2b = fma2(f2[j], f2[j], ss2b);
+            else ss2 = fma2(f2[j], f2[j], ss2);
+            if constexpr (KEEP_F32) xf[i][j] = f2[j];
+          }
         }
       }
       ss2 = add2(ss2, ss2b);
