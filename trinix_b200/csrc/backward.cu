@@ -1,6 +1,6 @@
 // Backward of the row and gate ops: RMSNorm, LayerNorm (dx, dW, db) and the three GLUs.
 //
-// Norms. A CTA of 256 or 512 threads walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; a row of x and
+// Norms. A CTA of 128 to 512 threads walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; a row of x and
 // of dy is read from HBM once with 128-bit streaming loads and stays in registers. The row's
 // statistics are recomputed from x (nothing has to be saved by the forward), dx is written, and
 // every thread keeps fp32 running sums of dy * n (and dy) for the columns it owns. At the end
@@ -17,7 +17,7 @@
 // written straight into the halves of a concatenated (R, 2H) gradient.
 #include "common.cuh"
 
-// vectors per thread for rows of 257..512 vectors (512 / this many threads per row)
+// RMSNorm: vectors per thread for rows of 257..512 vectors (512 / this many threads per row)
 #ifndef TRX_BWD512_VPT
 #define TRX_BWD512_VPT 2
 #endif
@@ -25,7 +25,7 @@
 #ifndef TRX_BWD_L2_PREFETCH
 #define TRX_BWD_L2_PREFETCH 1
 #endif
-// minimum resident 256-thread CTAs per SM asked of the compiler (caps registers per thread);
+// minimum resident CTAs (of up to 256 threads) per SM asked of the compiler (caps registers per thread);
 // without it the compiler spends registers freely and the occupancy drops (measured: LayerNorm
 // 336 us at 121 registers, 208 us at 80)
 #ifndef TRX_BWD_MINB_LN
@@ -119,7 +119,7 @@ __device__ __forceinline__ float act_grad(int act, float z) {
 }
 
 template <bool LN, typename T, int VPT, int NT>
-__global__ void __launch_bounds__(NT, NT == 256 ? (LN ? TRX_BWD_MINB_LN : TRX_BWD_MINB_RMS) : 1) norm_bwd_kernel(const NormBwdParams p) {
+__global__ void __launch_bounds__(NT, NT <= 256 ? (LN ? TRX_BWD_MINB_LN : TRX_BWD_MINB_RMS) : 1) norm_bwd_kernel(const NormBwdParams p) {
   using P = Pack<T>;
   constexpr int VEC = P::VEC;
   __shared__ float2 red[2][NT / 32];
@@ -452,7 +452,14 @@ static int launch_norm_bwd(NormBwdParams p, void* dw, void* db, float* ws, cudaS
     if (vec_ok && nvec <= 1024) {
       // few vectors per thread: the running column sums cost 8 (16 for LayerNorm) registers each
       if (nvec <= 256) launch_norm_bwd_vec<LN, T, 1, 256>(p, P_rows, stream);
-      else if (nvec <= 512) launch_norm_bwd_vec<LN, T, TRX_BWD512_VPT, 512 / TRX_BWD512_VPT>(p, P_rows, stream);
+      else if (nvec <= 512) {
+        // measured on 32768 x 4096 bf16: RMSNorm 256 threads x 2 vectors (146 us; 159 us at
+        // 128 x 4), LayerNorm 128 x 4 (170 us; 188 us at 256 x 2): LayerNorm has three CTA-wide
+        // reductions per row, which four warps finish sooner than eight; 512 threads x 1 vector
+        // is slower for both (213 / 278 us)
+        if constexpr (LN) launch_norm_bwd_vec<LN, T, 4, 128>(p, P_rows, stream);
+        else launch_norm_bwd_vec<LN, T, TRX_BWD512_VPT, 512 / TRX_BWD512_VPT>(p, P_rows, stream);
+      }
       else launch_norm_bwd_vec<LN, T, 2, 512>(p, P_rows, stream);
     } else {
       const int64_t cap = static_cast<int64_t>(sm_count_of_current_device()) * 8;
