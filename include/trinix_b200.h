@@ -1,5 +1,6 @@
 /*
- * trinix_b200 — C ABI of the sm_100a (B200) backend for Trinix's layer forward path.
+ * trinix_b200 — C ABI of the sm_100a (B200) backend for Trinix's layer hot path: the forward of
+ * the norms, int8 ops, RoPE, GLUs and attention, and the backward of the norms, GLUs and RoPE.
  *
  * Every entry point is `extern "C"`, takes plain device pointers, sizes and
  * strides (in ELEMENTS unless a name ends in `_bytes`), enqueues work on the
