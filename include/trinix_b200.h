@@ -336,6 +336,20 @@ int trx_attn_fwd_mask(const void* q, const void* k, const void* v, void* out, fl
                       void* stream);
 
 /*
+ * Status word of an attention workspace, read without synchronising. `host_word` is host
+ * memory the caller keeps alive across calls (pinned memory keeps the copy asynchronous),
+ * zero before the first call. If *host_word — as copied there by an earlier call — is already
+ * non-zero, a kernel gave up on a bounded wait and every later launch on that workspace has
+ * skipped its work: the call returns TRX_ERR_DEVICE_STATUS and enqueues nothing; the caller
+ * zeroes the device word and *host_word before using the workspace again. Otherwise a 4-byte
+ * copy of the device word into *host_word is enqueued on `stream`, behind the launches already
+ * there. Call it after each trx_attn_fwd / trx_attn_fwd_mask (or every few).
+ * Replaces nothing in the reference: there the failure path is the silent PyTorch fallback of
+ * trinix/layers/attention/base.py:435-439.
+ */
+int trx_attn_status(const void* workspace, unsigned int* host_word, void* stream);
+
+/*
  * trx_attn_fwd for callers that cannot provide a workspace. No counterpart in the reference.
  *
  * Who needs it: hosts that pass pointers in but cannot create device memory when the call is
@@ -351,6 +365,9 @@ int trx_attn_fwd_mask(const void* q, const void* k, const void* v, void* out, fl
  * Limit: the static block is 256 bytes, which is what the kernel needs for EVERY problem size
  * trx_attn_fwd accepts; if the library's own requirement ever exceeds the block the call
  * returns TRX_ERR_WORKSPACE and launches nothing.
+ * Arguments are checked before the block is cleared, so an argument error enqueues nothing.
+ * The one error that can follow the launch is TRX_ERR_CUDA from the 4-byte copy into
+ * status_out_or_null; the attention output is valid all the same.
  * The first call on each device looks up the block's device address (with that device
  * current); make that first call outside of any stream capture.
  * All calls on a device share the one block, which still holds the previous call's contents:

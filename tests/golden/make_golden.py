@@ -1,6 +1,6 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE itself.
 
-    PYTHONPATH=/path/to/trinix-reference python tests/golden/make_golden.py
+    TRINIX_REFERENCE=/path/to/trinix-reference python tests/golden/make_golden.py
 
 Imports the unmodified reference package (Trinix 0.1.4), runs its PyTorch backend on CPU
 (no CUDA here, so every module takes `_pytorch_forward`) on small seeded inputs and stores
@@ -13,7 +13,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("TRINIX_REFERENCE", "/root/reference")
+REF = os.environ.get("TRINIX_REFERENCE")
+if not REF or not os.path.isdir(os.path.join(REF, "trinix")):
+    raise SystemExit("set TRINIX_REFERENCE to a checkout of the reference (the folder holding trinix/)")
 sys.path.insert(0, REF)
 
 import trinix  # noqa: E402

@@ -84,6 +84,52 @@ def test_rope_and_attention_argument_validation(lib):
                             None) == 0  # empty batch
 
 
+def test_status_entry_point_validates_without_a_device(lib):
+    P = ctypes.c_void_p
+    word = ctypes.c_uint(0)
+    assert lib.trx_attn_status(None, ctypes.byref(word), None) == -1
+    assert lib.trx_attn_status(P(4096), None, None) == -1
+    word.value = 4  # a failure seen by an earlier copy: reported, nothing enqueued
+    assert lib.trx_attn_status(P(4096), ctypes.byref(word), None) == -8
+    assert word.value == 4
+
+
+def test_two_host_threads_on_first_use(lib):
+    """The library keeps a few per-device caches (driver entry point, occupancy answers, the
+    dynamic shared-memory attribute). Two host threads that make their first calls at the same
+    moment must get the same, correct status codes; the validation-only paths below reach the
+    shared state behind `make_map` without launching anything."""
+    import threading
+    P = ctypes.c_void_p
+    one, ws, st = P(4096), P(4096), I64x3(64, 8, 8)
+    a = (one, one, one, one, None, None)
+    results = [[], []]
+    start = threading.Barrier(2)
+
+    def work(slot):
+        start.wait()
+        for _ in range(200):
+            results[slot].append((
+                lib.trx_attn_fwd(*a, 1, 8, 8, 4, 3, 128, st, st, st, st, 1.0, 0, -1, -1, 2, ws, 256,
+                                 None),
+                lib.trx_attn_fwd(*a, 1, 8, 8, 4, 2, 128, I64x3(64, 8, 3), st, st, st, 1.0, 0, -1,
+                                 -1, 2, ws, 256, None),   # reaches make_map: stride not 16-byte
+                lib.trx_rmsnorm_fwd(one, one, one, None, 4, 8, 4, 8, 1e-6, 2, 2, None),
+                lib.trx_attn_fwd_static_scratch(*a, 1, 8, 8, 4, 2, 96, st, st, st, st, 1.0, 0, -1,
+                                                -1, 2, None, None),
+            ))
+
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    assert results[0] == results[1]
+    first = results[0][0]
+    assert first[0] == -3 and first[2] == -5 and first[1] in (-4, -7) and first[3] in (-6, -7)
+    assert all(r == first for r in results[0])
+
+
 def test_product_does_not_import_the_oracle():
     """No module of the product package may reach into oracle/ or the scratch folder."""
     pkg = os.path.join(os.path.dirname(HEADER), "..", "trinix_b200")

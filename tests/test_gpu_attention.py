@@ -238,22 +238,84 @@ def test_dense_mask_rejects_bad_shapes(cuda):
         T.triton_attn_func(q, k, v, attn_mask=torch.zeros(1, 1, 1, 128, 128, device=cuda))
 
 
-def test_launch_after_recorded_failure_is_skipped_until_cleared(cuda):
+def test_launch_after_recorded_failure_raises_then_recovers(cuda):
     """A non-zero status word (a bounded wait gave up in some earlier launch) makes every later
-    launch return at once, its on-chip resources released; reading the word clears it and the
-    kernel works again."""
+    launch skip its work on the device. The host learns of it without a synchronisation: every
+    attention call queues a 4-byte copy of the word into pinned memory and the next call checks
+    that copy first, raising status -8 instead of handing back unwritten output. The word is set
+    from the host here; no wait on the device is ever made to run out."""
     from trinix_b200 import ops
     q, k, v = (t.to(cuda) for t in _qkv(1, 512, 512, 4, 2, 128, seed=21))
     good = T.attention(q, k, v, causal=True)
     assert T.attention_status(cuda) == 0
     ops._workspace(cuda)[:4].view(torch.int32).fill_(4)     # as if a softmax wait had run out
-    for _ in range(3):                                       # skipped launches, several in a row
-        T.attention(q, k, v, causal=True)
+    T.attention(q, k, v, causal=True)                        # skipped on the device; copy queued
     torch.cuda.synchronize(cuda)
-    assert T.attention_status(cuda) == 4                     # reported once, then cleared
+    with pytest.raises(T._lib.TrinixB200Error) as e:         # first call that can know: raises
+        T.attention(q, k, v, causal=True)
+    assert e.value.code == -8 and "0x4" in str(e.value)
+    again = T.attention(q, k, v, causal=True)                # both copies were cleared
     assert T.attention_status(cuda) == 0
-    again = T.attention(q, k, v, causal=True)
     assert torch.equal(again, good)
+    # the C-level form of the same check
+    import ctypes
+    lib = T._lib.load()
+    host = torch.zeros(1, dtype=torch.int32).pin_memory()
+    ws = ops._workspace(cuda)
+    P = ctypes.c_void_p
+    st = P(torch.cuda.current_stream(cuda).cuda_stream)
+    ws[:4].view(torch.int32).fill_(2)
+    assert lib.trx_attn_status(P(ws.data_ptr()), P(host.data_ptr()), st) == 0
+    torch.cuda.synchronize(cuda)
+    assert int(host[0]) == 2
+    assert lib.trx_attn_status(P(ws.data_ptr()), P(host.data_ptr()), st) == -8
+    assert lib.trx_attn_status(None, P(host.data_ptr()), st) == -1
+    assert T.attention_status(cuda) == 2 and T.attention_status(cuda) == 0
+
+
+def test_views_the_tensor_maps_cannot_take_are_materialised(cuda):
+    """Legal strided views whose base is not 16-byte aligned or whose strides are not multiples
+    of 8 elements (a slice along D at an offset of 4, a head stride of 132) run all the same."""
+    g = torch.Generator().manual_seed(5)
+    big = torch.randn(2, 200, 4, 136, generator=g).bfloat16().to(cuda)
+    q, k, v = big[..., 4:132], big[..., 4:132].clone(), big[..., 8:136]
+    assert q.data_ptr() % 16 != 0 and q.stride(-1) == 1
+    out = T.triton_attn_func(q, k, v, causal=True)
+    ref = T.triton_attn_func(q.contiguous(), k, v.contiguous(), causal=True)
+    assert T.attention_status(cuda) == 0 and torch.equal(out, ref)
+    odd = torch.randn(1, 150, 2, 132, generator=g).bfloat16().to(cuda)[..., :128]
+    assert odd.stride(2) % 8 != 0
+    out = T.triton_attn_func(odd, odd, odd)
+    assert torch.equal(out, T.triton_attn_func(*(odd.contiguous(),) * 3))
+
+
+def test_flash_stand_in_keeps_the_conventions_of_the_symbol_it_replaces(cuda):
+    """flash_attn_func (the symbol bound at trinix/layers/attention/base.py:10-16): causal with
+    Sq < Sk is aligned bottom-right (decode against a KV cache sees every cached key), unknown
+    keywords raise instead of being dropped."""
+    Sq, Sk = 70, 300
+    q, k, v = _qkv(2, Sq, Sk, 4, 2, 128, seed=9)
+    out = T.flash_attn_func(q.to(cuda), k.to(cuda), v.to(cuda), causal=True)
+    assert T.attention_status(cuda) == 0
+    i, j = torch.arange(Sq)[:, None], torch.arange(Sk)[None, :]
+    mask = torch.zeros(Sq, Sk).masked_fill_(j > i + (Sk - Sq), float("-inf"))
+    kt, vt = k.repeat_interleave(2, 2), v.repeat_interleave(2, 2)
+    ref32 = R.attention_ref(q.float(), kt.float(), vt.float(), None, False, mask)
+    assert float((out.float().cpu() - ref32).abs().max()) <= TOL
+    # one query row against the cache: sees all keys
+    out1 = T.flash_attn_func(q[:, :1].to(cuda), k.to(cuda), v.to(cuda), causal=True)
+    full = T.triton_attn_func(q[:, :1].to(cuda), k.to(cuda), v.to(cuda), causal=False)
+    assert torch.equal(out1, full)
+    # equal lengths: identical to triton_attn_func
+    q2, k2, v2 = (t.to(cuda) for t in _qkv(1, 200, 200, 4, 4, 64, seed=2))
+    assert torch.equal(T.flash_attn_func(q2, k2, v2, causal=True),
+                       T.triton_attn_func(q2, k2, v2, causal=True))
+    assert torch.equal(T.flash_attn_func(q2, k2, v2, window_size=(50, 0)),
+                       T.triton_attn_func(q2, k2, v2, window_size=(50, 0)))
+    with pytest.raises(TypeError):
+        T.flash_attn_func(q2, k2, v2, softcap=30.0)
+    with pytest.raises(NotImplementedError):
+        T.flash_attn_func(q.to(cuda), k.to(cuda), v.to(cuda), causal=True, window_size=(10, 0))
 
 
 @pytest.mark.parametrize("Sq,Sk", [(1, 1000), (1, 128), (7, 2049), (130, 64)])

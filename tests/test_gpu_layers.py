@@ -124,26 +124,6 @@ def test_decoder_layer_int8_weights_matches_oracle(cuda, kernel_type, tile_kv):
     assert rel_err(y.cpu(), ref, floor_frac=1.0) <= 1e-1
 
 
-def test_patched_reference_modules_if_installed(cuda):
-    """With the reference package importable, install() makes ITS modules use these kernels."""
-    try:
-        with warnings.catch_warnings():
-            warnings.simplefilter("ignore")
-            import trinix  # noqa: F401
-    except ImportError:
-        pytest.skip("reference package not installed on this machine")
-    T.install(strict=True)
-    try:
-        from trinix import FastRMSNorm, FastSwiGLU
-        x = torch.randn(8, 4096, device=cuda, dtype=torch.bfloat16)
-        m = FastRMSNorm(4096).to(cuda).bfloat16()
-        assert rel_err(m(x).cpu(), R.rmsnorm_ref(x.cpu(), torch.ones(4096).bfloat16(), 1e-6)) <= 1e-2
-        xg = torch.randn(8, 2048, device=cuda, dtype=torch.bfloat16)
-        assert rel_err(FastSwiGLU(1024)(xg).cpu(), R.swiglu_ref(xg.cpu())) <= 1e-2
-    finally:
-        T.uninstall()
-
-
 def test_fused_rmsnorm_int8_module_equals_the_two_modules(cuda):
     """fuse(FastRMSNorm, RowwiseInt8Quant) runs one kernel and returns exactly what the two
     modules return one after the other."""

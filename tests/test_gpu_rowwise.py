@@ -230,6 +230,42 @@ def test_residual_rmsnorm_golden_and_shapes(cuda):
             assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 2e-3
 
 
+@pytest.mark.parametrize("xdtype,wdtype", [(torch.bfloat16, torch.float32),
+                                           (torch.float16, torch.float32),
+                                           (torch.bfloat16, torch.float16)])
+def test_residual_rmsnorm_weight_of_another_dtype(cuda, xdtype, wdtype):
+    """16-bit x and residual with a weight of another dtype (the state of a freshly built
+    FastFusedResidualRMSNorm under autocast-style use: fp32 ones). The normalised row must be the
+    fp32 SUM x + r, on the vector path (4096, 2048 columns) and on the scalar path (odd widths),
+    for the plain and the int8 form."""
+    g = torch.Generator().manual_seed(31)
+    for rows, cols in [(64, 4096), (9, 2048), (5, 777), (3, 8200), (2, 33000)]:
+        x = torch.randn(rows, cols, generator=g).to(xdtype)
+        r = (torch.randn(rows, cols, generator=g) * 3).to(xdtype)
+        w = (1 + 0.1 * torch.randn(cols, generator=g)).to(wdtype)
+        xc, rc, wc = x.to(cuda), r.to(cuda), w.to(cuda)
+        y, s = T.ops.residual_rmsnorm(xc, rc, wc, 1e-6, return_sum=True)
+        # the oracle's product is promoted to the wider dtype; the kernel rounds it once to x's
+        ref = R.residual_rmsnorm_ref(x, r, w, 1e-6).to(xdtype)
+        assert y.dtype == xdtype
+        assert rel_err(y.cpu(), ref) <= 1e-2
+        assert float((y.cpu() != ref).float().mean()) < 2e-3
+        assert torch.equal(s.cpu(), (x.float() + r.float()).to(xdtype))
+        codes, scales = T.residual_rmsnorm_quantize(xc, rc, wc, 1e-6)
+        c2, s2 = T.quantize_rowwise(y)
+        assert torch.equal(codes, c2) and torch.equal(scales, s2)
+    # the mirror module with its default fp32 weight on bf16 activations
+    m = T.FastFusedResidualRMSNorm(4096).to(cuda)
+    assert m.weight.dtype == torch.float32
+    x = torch.randn(16, 4096, generator=g).bfloat16()
+    r = (torch.randn(16, 4096, generator=g) * 2).bfloat16()
+    with torch.no_grad():
+        y = m(x.to(cuda), r.to(cuda))
+    y = y[0] if isinstance(y, tuple) else y
+    ref = R.residual_rmsnorm_ref(x, r, torch.ones(4096), 1e-6)
+    assert rel_err(y.float().cpu(), ref.float()) <= 1e-2
+
+
 def _assert_resln_close(y, x, r, w, b, eps=1e-5):
     """LayerNorm(x + r) against the oracle. fp32: 1e-5 relative. 16-bit: the kernel follows the
     oracle's rounding order round(round(w * round(n)) + b); the statistics can differ in their

@@ -10,10 +10,10 @@ import torch
 import trinix_b200 as T
 from oracle import reference_port as R
 from trinix_b200 import sharding
-from tests.util import Golden, bf16_ulps
+from tests.util import Golden, bf16_ulps, reference_path
 
 G = Golden()
-REFERENCE_DIR = os.environ.get("TRINIX_REFERENCE", "/root/reference")
+REFERENCE_DIR = reference_path() or ""
 no_cuda = not torch.cuda.is_available()
 
 

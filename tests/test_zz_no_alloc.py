@@ -19,10 +19,11 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-2  # the attention tolerance used throughout the suite (max abs, bf16)
 
 
-def _call(lib, fn_name, q, k, v, causal, window, slopes, extra):
+def _call(lib, fn_name, q, k, v, causal, window, slopes, extra, out=None):
     B, Sq, Hq, D = q.shape
     Sk, Hk = k.shape[1], k.shape[2]
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
     P = ctypes.c_void_p
     wl, wr = window if window is not None else (-1, -1)
     args = [P(q.data_ptr()), P(k.data_ptr()), P(v.data_ptr()), P(out.data_ptr()), None,
@@ -45,6 +46,7 @@ def test_static_scratch_attention_matches_workspace_attention_twice(cuda):
         (700, 700, 8, 2, 128, True, None, False),
         (520, 520, 4, 1, 64, False, (100, 0), True),
     ]
+    free_before = None
     with torch.cuda.device(cuda):
         for Sq, Sk, Hq, Hk, D, causal, window, alibi in cases:  # two calls in a row
             q = torch.randn(2, Sq, Hq, D, generator=g).bfloat16().to(cuda)
@@ -55,9 +57,19 @@ def test_static_scratch_attention_matches_workspace_attention_twice(cuda):
                 slopes = torch.tensor([2.0 ** (-(i + 1)) for i in range(Hq)], device=cuda)
             ref = _call(lib, "trx_attn_fwd", q, k, v, causal, window, slopes,
                         [P(ws.data_ptr()), ws.numel()])
-            got = _call(lib, "trx_attn_fwd_static_scratch", q, k, v, causal, window, slopes,
-                        [P(status.data_ptr())])
+            if free_before is None:
+                # the first call on a device looks up the block's address; device memory in use
+                # is compared around every call after that one
+                _call(lib, "trx_attn_fwd_static_scratch", q, k, v, causal, window, slopes,
+                      [P(status.data_ptr())])
+            got = torch.empty_like(q)   # the caller's output buffer exists before the call
             torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info(cuda)[0]   # cudaMemGetInfo: the driver's view
+            _call(lib, "trx_attn_fwd_static_scratch", q, k, v, causal, window, slopes,
+                  [P(status.data_ptr())], out=got)
+            torch.cuda.synchronize()
+            # "allocates nothing": the device has exactly as much free memory after the call
+            assert torch.cuda.mem_get_info(cuda)[0] >= free_before
             assert int(status.item()) == 0, "the kernel recorded a bounded-wait timeout"
             assert int(ws[:4].view(torch.int32).item()) == 0
             assert not torch.isnan(got.float()).any()

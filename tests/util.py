@@ -69,3 +69,14 @@ def outlier_matrix(rows: int, cols: int, seed: int = 0) -> torch.Tensor:
     x = torch.randn(rows, cols, generator=g)
     mask = torch.rand(rows, cols, generator=g) < 0.001
     return torch.where(mask, 20 * x, x)
+
+
+def reference_path():
+    """Where an unmodified copy of the reference package (a directory holding `trinix/`) can be
+    imported from: $TRINIX_REFERENCE, else the untracked install under baseline/_ref of this
+    checkout. None when neither exists."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for cand in (os.environ.get("TRINIX_REFERENCE"), os.path.join(root, "baseline", "_ref")):
+        if cand and os.path.isdir(os.path.join(cand, "trinix")):
+            return cand
+    return None

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libtrinix_b
 
 TRX_F32, TRX_F16, TRX_BF16 = 0, 1, 2
 GLU_SWIGLU, GLU_GEGLU_TANH, GLU_REGLU = 0, 1, 2
+TRX_ERR_DEVICE_STATUS = -8
 
 I64x3 = c_int64 * 3
 
@@ -76,6 +77,7 @@ SIGNATURES = {
                                   c_void_p, c_int, I64x3, c_int64, c_int64, c_int64, c_int64,
                                   c_int64, c_int64, I64x3, I64x3, I64x3, I64x3, c_float, c_int,
                                   c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
+    "trx_attn_status": (c_int, [c_void_p, c_void_p, c_void_p]),
     "trx_attn_fwd_static_scratch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                             c_int64, I64x3, I64x3, I64x3, I64x3, c_float, c_int,

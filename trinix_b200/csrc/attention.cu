@@ -23,6 +23,7 @@
 // own copies and MMAs (bounded again), frees its TMEM and returns.
 #include <cuda.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -955,16 +956,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 static EncodeTiledFn get_encode_fn() {
   static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  static std::once_flag once;  // host threads that race on the first call all see the result
+  std::call_once(once, [] {
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
             cudaSuccess &&
         qres == cudaDriverEntryPointSuccess)
       fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
+  });
   return fn;
 }
 
@@ -998,15 +998,18 @@ static int make_map(CUtensorMap* tm, const void* base, int is_bf16, int64_t D, i
 
 template <int D, bool BF16, bool BIAS>
 static int launch_attn_bias(const AttnParams& p, cudaStream_t stream) {
-  static bool configured[64] = {false};
+  // The attribute is set once per device; host threads that race on the first call each set
+  // the same value (the call is idempotent) and publish the flag atomically.
+  static std::atomic<bool> configured[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return TRX_ERR_CUDA;
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
+  const bool cacheable = dev >= 0 && dev < 64;
+  if (!cacheable || !configured[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(attn_fwd_kernel<D, BF16, BIAS>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                              AttnSmem<D>::DYN_BYTES) != cudaSuccess)
       return TRX_ERR_CUDA;
-    configured[dev] = true;
+    if (cacheable) configured[dev].store(true, std::memory_order_release);
   }
   const int mblocks = (p.Sq + ATT_NQ * ATT_BM - 1) / (ATT_NQ * ATT_BM);
   dim3 grid(mblocks, p.Hq, p.B);
@@ -1026,15 +1029,18 @@ using namespace trx;
 
 extern "C" size_t trx_attn_workspace_bytes(void) { return 256; }
 
-// Shared body of the attention entry points. `bias` may be null (no dense mask).
-static int attn_fwd_impl(const void* q, const void* k, const void* v, void* out,
-                         float* lse_or_null, const float* slopes_or_null, const void* bias,
-                         int bias_dtype, const int64_t* bias_strides, int64_t B, int64_t Sq,
-                         int64_t Sk, int64_t Hq, int64_t Hk, int64_t D,
-                         const int64_t q_strides[3], const int64_t k_strides[3],
-                         const int64_t v_strides[3], const int64_t o_strides[3], float scale,
-                         int causal, int64_t window_left, int64_t window_right, int dtype,
-                         void* workspace, size_t workspace_bytes, void* stream) {
+// Validation and parameter block shared by the attention entry points; nothing is enqueued.
+// `bias` may be null (no dense mask). Returns TRX_OK with *nothing_to_do set for empty problems.
+static int attn_fwd_prepare(AttnParams& p, bool* nothing_to_do, const void* q, const void* k,
+                            const void* v, void* out, float* lse_or_null,
+                            const float* slopes_or_null, const void* bias, int bias_dtype,
+                            const int64_t* bias_strides, int64_t B, int64_t Sq, int64_t Sk,
+                            int64_t Hq, int64_t Hk, int64_t D, const int64_t q_strides[3],
+                            const int64_t k_strides[3], const int64_t v_strides[3],
+                            const int64_t o_strides[3], float scale, int causal,
+                            int64_t window_left, int64_t window_right, int dtype,
+                            void* workspace, size_t workspace_bytes) {
+  *nothing_to_do = false;
   if (dtype != TRX_BF16 && dtype != TRX_F16) return TRX_ERR_DTYPE;
   if (bias) {
     if (bias_dtype != TRX_F32 && bias_dtype != dtype) return TRX_ERR_DTYPE;
@@ -1046,7 +1052,10 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* out,
   if (Hq % Hk != 0) return TRX_ERR_SHAPE;
   if (D != 64 && D != 128) return TRX_ERR_UNSUPPORTED;
   if ((window_left < 0) != (window_right < 0)) return TRX_ERR_SHAPE;
-  if (B == 0 || Sq == 0) return TRX_OK;
+  if (B == 0 || Sq == 0) {
+    *nothing_to_do = true;
+    return TRX_OK;
+  }
   if (!q || !out || !q_strides || !k_strides || !v_strides || !o_strides)
     return TRX_ERR_NULL_POINTER;
   if (Sk > 0 && (!k || !v)) return TRX_ERR_NULL_POINTER;
@@ -1061,7 +1070,7 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* out,
     if (q_strides[i] < 0 || k_strides[i] < 0 || v_strides[i] < 0 || o_strides[i] < 0)
       return TRX_ERR_STRIDE;
 
-  AttnParams p{};
+  p = AttnParams{};
   const int is_bf16 = dtype == TRX_BF16;
   int rc = make_map(&p.tm_q, q, is_bf16, D, Sq, Hq, B, q_strides[0], q_strides[1], q_strides[2]);
   if (rc != TRX_OK) return rc;
@@ -1108,9 +1117,45 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* out,
     p.bias_sq = bias_strides[2];
     p.bias_kind = bias_dtype == TRX_F32 ? 1 : 2;
   }
+  return TRX_OK;
+}
+
+static int attn_fwd_launch(const AttnParams& p, int64_t D, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (D == 128) return is_bf16 ? launch_attn<128, true>(p, s) : launch_attn<128, false>(p, s);
-  return is_bf16 ? launch_attn<64, true>(p, s) : launch_attn<64, false>(p, s);
+  if (D == 128) return p.is_bf16 ? launch_attn<128, true>(p, s) : launch_attn<128, false>(p, s);
+  return p.is_bf16 ? launch_attn<64, true>(p, s) : launch_attn<64, false>(p, s);
+}
+
+static int attn_fwd_impl(const void* q, const void* k, const void* v, void* out,
+                         float* lse_or_null, const float* slopes_or_null, const void* bias,
+                         int bias_dtype, const int64_t* bias_strides, int64_t B, int64_t Sq,
+                         int64_t Sk, int64_t Hq, int64_t Hk, int64_t D,
+                         const int64_t q_strides[3], const int64_t k_strides[3],
+                         const int64_t v_strides[3], const int64_t o_strides[3], float scale,
+                         int causal, int64_t window_left, int64_t window_right, int dtype,
+                         void* workspace, size_t workspace_bytes, void* stream) {
+  AttnParams p;
+  bool nothing_to_do = false;
+  const int rc = attn_fwd_prepare(p, &nothing_to_do, q, k, v, out, lse_or_null, slopes_or_null,
+                                  bias, bias_dtype, bias_strides, B, Sq, Sk, Hq, Hk, D, q_strides,
+                                  k_strides, v_strides, o_strides, scale, causal, window_left,
+                                  window_right, dtype, workspace, workspace_bytes);
+  if (rc != TRX_OK || nothing_to_do) return rc;
+  return attn_fwd_launch(p, D, stream);
+}
+
+// Status word of a workspace, without a synchronisation. `host_word` is host memory the caller
+// keeps alive (pinned memory makes the copy asynchronous). If the word copied there by an
+// earlier call is already non-zero, a kernel gave up on a bounded wait: TRX_ERR_DEVICE_STATUS,
+// nothing is enqueued. Otherwise a 4-byte copy of the device word into *host_word is enqueued
+// on `stream`, behind the launches already there.
+extern "C" int trx_attn_status(const void* workspace, unsigned int* host_word, void* stream) {
+  if (!workspace || !host_word) return TRX_ERR_NULL_POINTER;
+  if (*reinterpret_cast<volatile unsigned int*>(host_word) != 0u) return TRX_ERR_DEVICE_STATUS;
+  if (cudaMemcpyAsync(host_word, workspace, sizeof(unsigned int), cudaMemcpyDeviceToHost,
+                      static_cast<cudaStream_t>(stream)) != cudaSuccess)
+    return TRX_ERR_CUDA;
+  return TRX_OK;
 }
 
 extern "C" int trx_attn_fwd(const void* q, const void* k, const void* v, void* out,
@@ -1186,14 +1231,22 @@ extern "C" int trx_attn_fwd_static_scratch(
   const int rc = static_scratch_for_current_device(&scratch);
   if (rc != TRX_OK) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // Every argument is checked before anything is enqueued: an argument error leaves the stream
+  // untouched.
+  AttnParams p;
+  bool nothing_to_do = false;
+  const int checked = attn_fwd_prepare(
+      p, &nothing_to_do, q, k, v, out, lse_or_null, slopes_or_null, nullptr, 0, nullptr, B, Sq, Sk,
+      Hq, Hk, D, q_strides, k_strides, v_strides, o_strides, scale, causal, window_left,
+      window_right, dtype, scratch, ATT_STATIC_SCRATCH_BYTES);
+  if (checked != TRX_OK || nothing_to_do) return checked;
   // The array keeps whatever the previous call left in it. The status word must start at
   // zero (a non-zero word makes the kernel skip its work), so clear the block in stream order.
   if (cudaMemsetAsync(scratch, 0, ATT_STATIC_SCRATCH_BYTES, s) != cudaSuccess) return TRX_ERR_CUDA;
-  const int launched =
-      trx_attn_fwd(q, k, v, out, lse_or_null, slopes_or_null, B, Sq, Sk, Hq, Hk, D, q_strides,
-                   k_strides, v_strides, o_strides, scale, causal, window_left, window_right, dtype,
-                   scratch, ATT_STATIC_SCRATCH_BYTES, stream);
+  const int launched = attn_fwd_launch(p, D, stream);
   if (launched != TRX_OK) return launched;
+  // The one error that can follow the launch: the runtime refusing the 4-byte status copy. The
+  // attention output is then valid all the same; only *status_out_or_null was not written.
   if (status_out_or_null != nullptr &&
       cudaMemcpyAsync(status_out_or_null, scratch, sizeof(unsigned int), cudaMemcpyDefault, s) !=
           cudaSuccess)

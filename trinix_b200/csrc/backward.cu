@@ -417,16 +417,18 @@ static int64_t norm_bwd_partial_rows(int64_t R, int64_t C) {
 // the number of rows of partial sums that were written.
 template <bool LN, typename T, int VPT, int NT>
 static void launch_norm_bwd_vec(const NormBwdParams& p, int64_t& P_rows, cudaStream_t stream) {
-  static int blocks_per_sm_of[64] = {0};
-  int dev = 0, uncached = 0;
+  static std::atomic<int> blocks_per_sm_of[64];  // racing first calls store the same value
+  int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
-  int& blocks_per_sm = (dev >= 0 && dev < 64) ? blocks_per_sm_of[dev] : uncached;
+  const bool cacheable = dev >= 0 && dev < 64;
+  int blocks_per_sm = cacheable ? blocks_per_sm_of[dev].load(std::memory_order_acquire) : 0;
   if (blocks_per_sm == 0) {
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, norm_bwd_kernel<LN, T, VPT, NT>, NT, 0) !=
             cudaSuccess || n <= 0)
       n = 1;
     blocks_per_sm = n;
+    if (cacheable) blocks_per_sm_of[dev].store(n, std::memory_order_release);
   }
   const int64_t resident = static_cast<int64_t>(sm_count_of_current_device()) * blocks_per_sm * TRX_BWD_WAVES;
   if (P_rows > resident) P_rows = resident;

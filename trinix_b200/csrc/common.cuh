@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/trinix_b200.h"
 
 namespace trx {
@@ -412,16 +414,16 @@ __device__ __forceinline__ uint32_t pack_low_bytes(uint32_t a, uint32_t b, uint3
 
 // SM count of the current device, cached per device ordinal.
 inline int sm_count_of_current_device() {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[64];  // racing first calls store the same value
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  int n = cached[dev].load(std::memory_order_acquire);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
       n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_release);
   }
-  return cached[dev];
+  return n;
 }
 
 inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

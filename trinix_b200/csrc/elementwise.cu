@@ -116,7 +116,8 @@ static int launch_glu(const void* up, const void* gate, void* y, int64_t R, int6
         static_cast<const T*>(up), static_cast<const T*>(gate), static_cast<T*>(y), R, nvec, us,
         gs, ys);
   } else {
-    const unsigned grid = static_cast<unsigned>(R < 148 * 8 ? R : 148 * 8);
+    const int64_t cap = static_cast<int64_t>(sm_count_of_current_device()) * 8;
+    const unsigned grid = static_cast<unsigned>(R < cap ? R : cap);
     glu_kernel_scalar<ACT, T><<<grid, 256, 0, stream>>>(
         static_cast<const T*>(up), static_cast<const T*>(gate), static_cast<T*>(y), R, H, us, gs,
         ys);
@@ -403,7 +404,8 @@ static int launch_dequant(const int8_t* codes, const float* scales, void* y, int
     dequant_kernel<T><<<grid, DQ_THREADS, 0, stream>>>(codes, scales, static_cast<T*>(y), R,
                                                        nvec16, cs, ys);
   } else {
-    const unsigned grid = static_cast<unsigned>(R < 148 * 8 ? R : 148 * 8);
+    const int64_t cap = static_cast<int64_t>(sm_count_of_current_device()) * 8;
+    const unsigned grid = static_cast<unsigned>(R < cap ? R : cap);
     dequant_kernel_scalar<T><<<grid, 256, 0, stream>>>(codes, scales, static_cast<T*>(y), R, C, cs,
                                                        ys);
   }

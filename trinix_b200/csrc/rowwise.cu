@@ -13,6 +13,7 @@
 // Rows that do not fit the vector path (columns not a multiple of the vector width,
 // unaligned pointers, more than 16384 vectors) take a scalar multi-pass kernel, so nothing
 // is ever truncated.
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -469,7 +470,16 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
             const int v = i * TPR + t;
             if (live(i)) {
               float f[VEC];
-              P::unpack(raw[i], f);
+              if constexpr (KEEP_F32) {
+                // residual forms of a 16-bit row: the fp32 sum x + r lives only in xf
+#pragma unroll
+                for (int j = 0; j < VEC / 2; ++j) {
+                  f[2 * j] = xf[i][j].x;
+                  f[2 * j + 1] = xf[i][j].y;
+                }
+              } else {
+                P::unpack(raw[i], f);
+              }
               const int64_t col = static_cast<int64_t>(v) * VEC;
               float wv[VEC];
               load_param_vec<VEC>(p.w, p.w_dtype, col, wv);
@@ -641,12 +651,13 @@ template <int OP, typename T, int TPR, int VPT, bool FULL>
 static int launch_cfg_full(const RowParams& p, cudaStream_t stream) {
   constexpr int BLOCK = TPR > 32 ? TPR : 256;
   constexpr int ROWS_PER_CTA = BLOCK / TPR;
-  // The occupancy answer is cached per device ordinal.
-  static int blocks_per_sm_of[64] = {0};
+  // The occupancy answer is cached per device ordinal. Host threads that race on the first
+  // call each compute the same value and store it atomically.
+  static std::atomic<int> blocks_per_sm_of[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return TRX_ERR_CUDA;
-  int uncached = 0;
-  int& blocks_per_sm = (dev >= 0 && dev < 64) ? blocks_per_sm_of[dev] : uncached;
+  const bool cacheable = dev >= 0 && dev < 64;
+  int blocks_per_sm = cacheable ? blocks_per_sm_of[dev].load(std::memory_order_acquire) : 0;
   if (blocks_per_sm == 0) {
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, row_kernel<OP, T, TPR, VPT, FULL>, BLOCK,
@@ -654,6 +665,7 @@ static int launch_cfg_full(const RowParams& p, cudaStream_t stream) {
         n <= 0)
       n = 1;
     blocks_per_sm = n;
+    if (cacheable) blocks_per_sm_of[dev].store(n, std::memory_order_release);
   }
   const int64_t need = (p.R + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
   const int64_t cap = static_cast<int64_t>(sm_count_of_current_device()) * blocks_per_sm;

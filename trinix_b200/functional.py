@@ -51,9 +51,46 @@ def triton_attn_func(
 
 
 def flash_attn_func(q, k, v, dropout_p: float = 0.0, softmax_scale: Optional[float] = None,
-                    causal: bool = False, **_unused) -> torch.Tensor:
+                    causal: bool = False, window_size: Tuple[int, int] = (-1, -1),
+                    alibi_slopes: Optional[torch.Tensor] = None, **unsupported) -> torch.Tensor:
     """Stand-in for the third-party symbol the reference binds at
     trinix/layers/attention/base.py:10-16 and calls at :338-344 (q, k, v, dropout_p, causal).
-    It runs the same sm_100a kernel, so kernel_type='flash' needs no flash-attn dispatch."""
+    It runs the same sm_100a kernel, so kernel_type='flash' needs no flash-attn dispatch.
+
+    It keeps the conventions of the symbol it replaces where they differ from
+    triton_attn_func: with causal=True and Sq != Sk the mask is aligned to the BOTTOM-RIGHT
+    corner (query i sees keys j <= i + Sk - Sq), which is what decoding against a KV cache
+    needs; window_size uses -1 for "unbounded" on either side; alibi_slopes is (H,) or (B, H)
+    with B == 1. Any other keyword of the original (softcap, deterministic, return_attn_probs,
+    ...) raises instead of being dropped silently."""
+    if unsupported:
+        live = {n: val for n, val in unsupported.items()
+                if not (val is None or val is False or (n == "softcap" and val == 0.0))}
+        if live:
+            raise TypeError(f"flash_attn_func stand-in does not support {sorted(live)}")
+    Sq, Sk = q.shape[1], k.shape[1]
+    wl, wr = (int(window_size[0]), int(window_size[1])) if window_size is not None else (-1, -1)
+    slopes = alibi_slopes
+    if slopes is not None and slopes.dim() == 2:
+        if slopes.shape[0] != 1:
+            raise NotImplementedError("per-batch alibi_slopes are not supported")
+        slopes = slopes[0]
+    if slopes is not None and Sq != Sk:
+        # the original measures ALiBi distances from the bottom-right aligned diagonal
+        raise NotImplementedError("flash_attn_func stand-in: alibi_slopes need Sq == Sk")
+    window = None
+    has_window = wl >= 0 or wr >= 0
+    if Sq != Sk and (causal or has_window):
+        # The original aligns the causal diagonal and the window to the bottom-right corner:
+        # query i sees keys j <= i + (Sk - Sq). Expressed through the kernel's window predicate
+        # -left <= j - i <= right with right = Sk - Sq, which needs Sk > Sq and no second window.
+        if has_window or Sk < Sq:
+            raise NotImplementedError(
+                "flash_attn_func stand-in: Sq != Sk is supported with causal=True, Sk > Sq and "
+                "no window_size only")
+        window = (1 << 29, Sk - Sq)
+        causal = False
+    elif has_window:
+        window = (wl if wl >= 0 else 1 << 29, wr if wr >= 0 else 1 << 29)
     return triton_attn_func(q, k, v, dropout_p=dropout_p, softmax_scale=softmax_scale,
-                            causal=causal)
+                            causal=causal, window_size=window, alibi_slopes=slopes)

@@ -285,6 +285,19 @@ def _bshd(t: torch.Tensor) -> torch.Tensor:
     return t if t.stride(-1) == 1 or t.numel() == 0 else t.contiguous()
 
 
+def _tma_view(t: torch.Tensor) -> torch.Tensor:
+    """A (B, S, H, D) view the attention kernel's tensor maps accept: unit head-dim stride, a
+    16-byte aligned base and batch / seq / head strides that are multiples of 8 elements (a
+    stride of 0, an expanded dim, is fine and stays as it is). Any other legal view (a slice
+    along D at an odd offset, a head stride of 100, ...) is materialised once."""
+    t = _bshd(t)
+    if t.numel() == 0:
+        return t
+    ok = t.data_ptr() % 16 == 0 and all(
+        t.shape[i] == 1 or t.stride(i) % 8 == 0 for i in range(3))
+    return t if ok else t.contiguous()
+
+
 def rope(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
          inverse: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """Half-split rotary embedding of q (B,S,Hq,D) and k (B,S,Hk,D) in one launch.
@@ -478,16 +491,47 @@ def layernorm_backward(dy: torch.Tensor, x: torch.Tensor, weight: Optional[torch
 
 # ----------------------------------------------------------------------------- attention
 _workspaces: dict = {}
+_status_host: dict = {}  # device index -> pinned int32[1] mirror of the status word
+
+
+def _dev_index(dev: torch.device) -> int:
+    return dev.index if dev.index is not None else torch.cuda.current_device()
 
 
 def _workspace(dev: torch.device) -> torch.Tensor:
-    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    idx = _dev_index(dev)
     ws = _workspaces.get(idx)
     if ws is None:
         n = int(_lib.load().trx_attn_workspace_bytes())
         ws = torch.zeros(n, dtype=torch.uint8, device=torch.device("cuda", idx))
         _workspaces[idx] = ws
+        _status_host[idx] = torch.zeros(1, dtype=torch.int32).pin_memory()
     return ws
+
+
+def _raise_if_failed(fn: str, dev: torch.device) -> None:
+    """Host-side check of the status word's pinned mirror; no synchronisation. The mirror holds
+    what the copy queued behind the most recent COMPLETED launch saw. Non-zero: a kernel gave up
+    on a bounded wait, and it and every launch after it skipped their work, leaving their outputs
+    unwritten. Both copies of the word are cleared (so that the next call runs again) and the
+    failure is raised; outputs returned since the failing launch must be discarded."""
+    host = _status_host[_dev_index(dev)]
+    word = int(host[0])
+    if word:
+        _workspace(dev)[:4].zero_()
+        host.zero_()
+        raise _lib.TrinixB200Error(
+            fn, _lib.TRX_ERR_DEVICE_STATUS,
+            f"{_lib.load().trx_status_string(_lib.TRX_ERR_DEVICE_STATUS).decode()} "
+            f"(status word {word:#x}); attention outputs produced since then are invalid")
+
+
+def _queue_status_copy(ws: torch.Tensor, dev: torch.device) -> None:
+    host = _status_host[_dev_index(dev)]
+    rc = _lib.load().trx_attn_status(_ptr(ws), ctypes.c_void_p(host.data_ptr()), _stream(dev))
+    if rc == _lib.TRX_ERR_DEVICE_STATUS:  # the mirror turned non-zero while this call ran
+        _raise_if_failed("trx_attn_status", dev)
+    _lib.check("trx_attn_status", rc)
 
 
 def attention_status(device=None) -> int:
@@ -495,9 +539,11 @@ def attention_status(device=None) -> int:
     bounded on-chip wait gave up in some earlier launch; the word is then cleared."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     ws = _workspace(dev)
-    word = int(ws[:4].view(torch.int32).item())
+    word = int(ws[:4].view(torch.int32).item())  # .item() waits for the stream
     if word:
         ws[:4].zero_()
+    torch.cuda.current_stream(dev).synchronize()
+    _status_host[_dev_index(dev)].zero_()
     return word
 
 
@@ -546,7 +592,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
     dev = _need_cuda(q, k, v, alibi_slopes, attn_mask)
     if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError("attention needs q, k, v of one dtype, bfloat16 or float16")
-    q, k, v = _bshd(q), _bshd(k), _bshd(v)
+    q, k, v = _tma_view(q), _tma_view(k), _tma_view(v)
     B, Sq, Hq, D = q.shape
     Bk, Sk, Hk, Dk = k.shape
     if (Bk, Dk) != (B, D) or v.shape != k.shape:
@@ -568,6 +614,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
     out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=dev)
     lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=dev) if return_lse else None
     ws = _workspace(dev)
+    # a failure recorded by an earlier launch surfaces here, before more work is queued
+    _raise_if_failed("trx_attn_fwd", dev)
     if attn_mask is not None:
         m, mstr = _dense_mask(attn_mask, B, Hq, Sq, Sk, q.dtype)
         with torch.cuda.device(dev):
@@ -577,7 +625,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
                 I64x3(*k.stride()[:3]), I64x3(*v.stride()[:3]), I64x3(*out.stride()[:3]),
                 float(scale), int(bool(causal)), wl, wr, _code(q), _ptr(ws), ws.numel(),
                 _stream(dev))
-        _lib.check("trx_attn_fwd_mask", rc)
+            _lib.check("trx_attn_fwd_mask", rc)
+            _queue_status_copy(ws, dev)
         _count()
         return (out, lse) if return_lse else out
     with torch.cuda.device(dev):
@@ -586,6 +635,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
                                       I64x3(*k.stride()[:3]), I64x3(*v.stride()[:3]),
                                       I64x3(*out.stride()[:3]), float(scale), int(bool(causal)),
                                       wl, wr, _code(q), _ptr(ws), ws.numel(), _stream(dev))
-    _lib.check("trx_attn_fwd", rc)
+        _lib.check("trx_attn_fwd", rc)
+        _queue_status_copy(ws, dev)
     _count()
     return (out, lse) if return_lse else out
