@@ -857,16 +857,17 @@ def main():
     cx = torch.where(torch.rand(cx.shape, generator=gc) < 0.001, 20 * cx, cx).bfloat16().to(device)
     cq = torch.randn(n_units, 512, 8, 128, generator=gc).bfloat16().to(device)
     ckv = torch.randn(n_units, 512, 2, 128, generator=gc).bfloat16().to(device)
+    cw = (1 + 0.02 * torch.randn(4096, generator=gc)).bfloat16().to(device)  # replicated weight
     cross = {
         "quantize": sharding.cross_rank_identical(lambda t: ops.quantize_rowwise(t), [cx], rank, world),
         "rmsnorm_quantize": sharding.cross_rank_identical(
-            lambda t: ops.rmsnorm_quantize(t, w, 1e-6), [cx], rank, world),
+            lambda t: ops.rmsnorm_quantize(t, cw, 1e-6), [cx], rank, world),
         "dequantize": sharding.cross_rank_identical(
             lambda t: ops.dequantize_rowwise(*ops.quantize_rowwise(t)), [cx], rank, world),
         "attention_causal": sharding.cross_rank_identical(
             lambda a, b_: ops.attention(a, b_, b_, causal=True), [cq, ckv], rank, world),
     }
-    del cx, cq, ckv
+    del cx, cq, ckv, cw
 
     # ---- end to end: pinned host buffers, copies inside the timed region -----------------------
     e2e = E2E(device, w, 99 + rank)
