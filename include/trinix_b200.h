@@ -336,6 +336,31 @@ int trx_attn_fwd_mask(const void* q, const void* k, const void* v, void* out, fl
                       void* stream);
 
 /*
+ * trx_attn_fwd_mask with dropout on the attention probabilities (mask_or_null may be NULL):
+ *   out = sum_j keep_ij * P_ij / (1 - p_eff) * V_j,   P = softmax(scale * Q K^T + bias)
+ * i.e. the probabilities are normalised first and dropped afterwards, the order of the reference's
+ * PyTorch backend (F.dropout on the softmax output, trinix/layers/attention/base.py:394-397); the
+ * LSE output is that of the undropped scores. The keep decision of element (b, h, i, j) is a pure
+ * function of (seed, offset, b, h, i, j): byte (j mod 16) of Philox4x32-10 with key
+ * (seed & 0xffffffff, seed >> 32) and counter (j / 16, i, b * Hq + h, offset), little-endian over
+ * the four result words; the element is dropped when that byte is below
+ * t = clamp(round(256 * dropout_p), 1, 255), so the realised probability is p_eff = t / 256 and
+ * kept elements are scaled by 256 / (256 - t). The stream can therefore be rebuilt on the host,
+ * which is how the tests check it element for element. 0 <= dropout_p < 1; 0 means no dropout.
+ * Replaces the dropout branch of the reference's kernel, trinix/kernels/attention_kernel.py:395-405
+ * (seed drawn at :526-532), whose own random stream (Triton's tl.rand) cannot be reproduced and
+ * whose normaliser, unlike its PyTorch backend's, includes the dropped probabilities.
+ */
+int trx_attn_fwd_dropout(const void* q, const void* k, const void* v, void* out,
+                         float* lse_or_null, const float* slopes_or_null, const void* mask_or_null,
+                         int mask_dtype, const int64_t mask_strides[3], int64_t B, int64_t Sq,
+                         int64_t Sk, int64_t Hq, int64_t Hk, int64_t D, const int64_t q_strides[3],
+                         const int64_t k_strides[3], const int64_t v_strides[3],
+                         const int64_t o_strides[3], float scale, int causal, int64_t window_left,
+                         int64_t window_right, int dtype, float dropout_p, uint64_t seed,
+                         uint32_t offset, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Status word of an attention workspace, read without synchronising. `host_word` is host
  * memory the caller keeps alive across calls (pinned memory keeps the copy asynchronous),
  * zero before the first call. If *host_word — as copied there by an earlier call — is already

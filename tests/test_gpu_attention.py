@@ -228,6 +228,83 @@ def test_dense_mask_combines_with_causal_and_alibi(cuda):
     assert err32 <= TOL and err <= TOL + noise, (err, err32, noise)
 
 
+@pytest.mark.parametrize("p_drop", [0.1, 0.5])
+@pytest.mark.parametrize("Sq,Sk,D,causal,with_mask", [(300, 300, 128, True, False),
+                                                      (257, 640, 64, False, True)])
+def test_dropout_matches_the_rebuilt_keep_mask(cuda, p_drop, Sq, Sk, D, causal, with_mask):
+    """dropout_p > 0: the kernel's Philox stream is rebuilt on the CPU element for element, so the
+    comparison with the reference's PyTorch arithmetic (softmax, then dropout, then times V,
+    base.py:394-397) is exact up to the usual tolerance, not statistical."""
+    B, Hq, Hk = 2, 4, 2
+    q, k, v = _qkv(B, Sq, Sk, Hq, Hk, D, seed=Sq + Sk + int(100 * p_drop))
+    mask = None
+    if with_mask:
+        mask = torch.randn(B, 1, Sq, Sk, generator=torch.Generator().manual_seed(5))
+    seed, offset = 0x1234_5678_9ABC_DEF0 >> 2, 3
+    out, lse = T.attention(q.to(cuda), k.to(cuda), v.to(cuda), causal=causal,
+                           attn_mask=None if mask is None else mask.to(cuda), dropout_p=p_drop,
+                           seed=seed, offset=offset, return_lse=True)
+    assert T.attention_status(cuda) == 0
+    keep = R.dropout_keep_mask_ref(seed, offset, B, Hq, Sq, Sk, p_drop)
+    g = Hq // Hk
+    kt, vt = k.repeat_interleave(g, dim=2), v.repeat_interleave(g, dim=2)
+    m4 = None if mask is None else mask.expand(B, Hq, Sq, Sk).contiguous()
+    ref32 = R.attention_dropout_ref(q.float(), kt.float(), vt.float(), None, causal, m4, keep, p_drop)
+    ref = R.attention_dropout_ref(q, kt, vt, None, causal,
+                                  None if m4 is None else m4.to(q.dtype), keep, p_drop).float()
+    o = out.float().cpu()
+    err32, err = float((o - ref32).abs().max()), float((o - ref).abs().max())
+    noise = float((ref - ref32).abs().max())
+    tol = TOL / (1.0 - p_drop)  # kept probabilities are scaled up by 1 / (1 - p)
+    assert err32 <= tol and err <= tol + noise, (err32, err, noise)
+    # the LSE is that of the undropped scores (another instantiation of the kernel computes it
+    # here, with its own rounding of the score arithmetic: close, not bit-equal)
+    _, lse0 = T.attention(q.to(cuda), k.to(cuda), v.to(cuda), causal=causal,
+                          attn_mask=None if mask is None else mask.to(cuda), return_lse=True)
+    torch.testing.assert_close(lse, lse0, rtol=1e-5, atol=1e-5)
+    # same seed and offset: the same result bit for bit; another offset: another mask
+    again = T.attention(q.to(cuda), k.to(cuda), v.to(cuda), causal=causal,
+                        attn_mask=None if mask is None else mask.to(cuda), dropout_p=p_drop,
+                        seed=seed, offset=offset)
+    other = T.attention(q.to(cuda), k.to(cuda), v.to(cuda), causal=causal,
+                        attn_mask=None if mask is None else mask.to(cuda), dropout_p=p_drop,
+                        seed=seed, offset=offset + 1)
+    assert torch.equal(again, out) and not torch.equal(other, out)
+
+
+def test_dropout_keep_rate_and_module_path(cuda):
+    """Statistics of the stream (v = 1 makes the output the kept mass of each row), and the
+    module surface: training mode drops, eval mode does not, the seed follows torch.manual_seed."""
+    B, S, H, D = 1, 2048, 2, 64
+    q = torch.zeros(B, S, H, D, dtype=torch.bfloat16, device=cuda)       # uniform probabilities
+    v = torch.ones(B, S, H, D, dtype=torch.bfloat16, device=cuda)
+    for p_drop in (0.1, 0.5):
+        out = T.attention(q, q, v, dropout_p=p_drop, seed=99)
+        thr = R.dropout_threshold(p_drop)
+        # every row: sum_j keep_j / (S * (1 - p_eff)), mean 1, std sqrt(p / ((1 - p) S))
+        m = out.float()[..., 0]
+        assert abs(float(m.mean()) - 1.0) < 5e-3
+        p_eff = thr / 256.0
+        assert abs(float(m.std()) - (p_eff / ((1 - p_eff) * S)) ** 0.5) < 5e-3
+    attn = T.FastGroupedQueryAttention(512, 8, 2, dropout=0.3, bias=False, kernel_type="triton",
+                                       causal=True).to(cuda).bfloat16()
+    x = torch.randn(2, 256, 512, device=cuda, dtype=torch.bfloat16)
+    with torch.no_grad():
+        attn.eval()
+        e1, e2 = attn(x)[0], attn(x)[0]
+        attn.train()
+        torch.manual_seed(5)
+        t1 = attn(x)[0]
+        t2 = attn(x)[0]
+        torch.manual_seed(5)
+        t3 = attn(x)[0]
+    assert torch.equal(e1, e2) and not torch.equal(t1, e1)
+    assert not torch.equal(t1, t2) and torch.equal(t1, t3)
+    assert T.attention_status(cuda) == 0
+    with pytest.raises(ValueError):
+        T.attention(q, q, v, dropout_p=1.0)
+
+
 def test_dense_mask_rejects_bad_shapes(cuda):
     q, k, v = (t.to(cuda) for t in _qkv(2, 128, 128, 2, 2, 64))
     with pytest.raises(ValueError):

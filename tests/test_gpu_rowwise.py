@@ -425,3 +425,29 @@ def test_rmsnorm_activation_golden_and_shapes(cuda, act):
     assert rel_err(ym.cpu(), R.rmsnorm_activation_ref(xm, m.weight.detach().cpu(), 1e-6, act)) <= 1e-2
     with pytest.raises(ValueError):
         T.ops.rmsnorm_activation(xm.to(cuda), m.weight, 1e-6, "gelu")
+
+
+def test_fused_int8_many_rows_odd_count(cuda):
+    """Many rows of the benchmark width (4096 bf16 columns, the guard-free specialisation, every
+    CTA striding over several rows) with a row count that divides by nothing: fused equals
+    unfused bit for bit, the oracle's quantiser agrees on the kernel's norm, and a sample of rows
+    matches the end-to-end oracle."""
+    R_, C_ = 24001, 4096
+    g = torch.Generator(device=cuda).manual_seed(77)
+    x = (torch.randn(R_, C_, generator=g, device=cuda) * 1.7).bfloat16()
+    w = (1 + 0.1 * torch.randn(C_, generator=g, device=cuda)).bfloat16()
+    codes, scales = T.rmsnorm_quantize(x, w, 1e-6)
+    y = T.ops.rmsnorm(x, w, 1e-6)
+    c2, s2 = T.quantize_rowwise(y)
+    assert torch.equal(codes, c2) and torch.equal(scales, s2)
+    # a strided input (row stride > C) takes the same path
+    big = torch.zeros(R_, C_ + 64, device=cuda, dtype=torch.bfloat16)
+    big[:, :C_] = x
+    c3, s3 = T.rmsnorm_quantize(big[:, :C_], w, 1e-6)
+    assert torch.equal(c3, codes) and torch.equal(s3, scales)
+    rows = torch.tensor([0, 1, 2, 777, 5919, 5920, 11840, 17760, 23679, 23680, 24000], device=cuda)
+    rc, rs = R.quantize_rowwise_ref(y[rows].cpu())
+    assert torch.equal(codes[rows].cpu(), rc) and torch.equal(scales[rows].cpu(), rs)
+    ref_c, ref_s = R.rmsnorm_quantize_ref(x[rows].cpu(), w.cpu(), 1e-6)
+    assert int((codes[rows].cpu().int() - ref_c.int()).abs().max()) <= 1
+    torch.testing.assert_close(scales[rows].cpu(), ref_s, rtol=1e-2, atol=0)

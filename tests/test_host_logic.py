@@ -109,7 +109,7 @@ def test_module_error_behaviour_matches_reference():
         T.FastGroupedQueryAttention(64, 4, 3)
     with pytest.raises(ValueError, match="CUDA"):  # a mask does not open a CPU path
         T.TritonAttentionKernel.apply(*([torch.zeros(1, 1, 1, 64)] * 3), attn_mask=torch.zeros(1, 1))
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError, match="CUDA"):  # nor does dropout
         T.TritonAttentionKernel.apply(*([torch.zeros(1, 1, 1, 64)] * 3), dropout_p=0.1)
 
 

@@ -186,3 +186,25 @@ def test_rope_gradient_is_the_inverse_rotation():
     assert int(bf16_ulps(dq, G("bwd_rope_dq")).max()) <= 1
     assert int(bf16_ulps(dk, G("bwd_rope_dk")).max()) <= 1
 
+
+
+def test_philox_known_answers_and_dropout_mask_shape():
+    """The generator behind the attention dropout stream, against the three known-answer vectors
+    its authors publish for Philox4x32 with 10 rounds, and the keep mask built from it."""
+    import numpy as np
+    kat = [((0, 0, 0, 0), (0, 0), "6627e8d5 e169c58d bc57ac4c 9b00dbd8"),
+           ((0xFFFFFFFF,) * 4, (0xFFFFFFFF,) * 2, "408f276d 41c83b0e a20bc7c6 6d5451fd"),
+           ((0x243F6A88, 0x85A308D3, 0x13198A2E, 0x03707344), (0xA4093822, 0x299F31D0),
+            "d16cfe09 94fdcceb 5001e420 24126ea1")]
+    for ctr, key, want in kat:
+        out = R.philox4x32_10(np.array(ctr, dtype=np.uint32), key)
+        assert " ".join("%08x" % int(v) for v in out) == want
+    assert [R.dropout_threshold(p) for p in (0.0, 0.001, 0.1, 0.5, 0.999)] == [0, 1, 26, 128, 255]
+    keep = R.dropout_keep_mask_ref(seed=1234, offset=7, B=2, H=3, Sq=40, Sk=50, dropout_p=0.25)
+    assert keep.shape == (2, 3, 40, 50) and keep.dtype == torch.bool
+    assert abs(float(keep.float().mean()) - 0.75) < 0.02
+    # a pure function of its arguments: another offset gives another mask, the same one the same
+    assert torch.equal(keep, R.dropout_keep_mask_ref(1234, 7, 2, 3, 40, 50, 0.25))
+    assert not torch.equal(keep, R.dropout_keep_mask_ref(1234, 8, 2, 3, 40, 50, 0.25))
+    # a longer key range extends the mask, it does not reshuffle it
+    assert torch.equal(keep, R.dropout_keep_mask_ref(1234, 7, 2, 3, 40, 64, 0.25)[..., :50])

@@ -8,7 +8,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_uint32, c_uint64, c_void_p
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libtrinix_b200.so")
 
@@ -77,6 +77,11 @@ SIGNATURES = {
                                   c_void_p, c_int, I64x3, c_int64, c_int64, c_int64, c_int64,
                                   c_int64, c_int64, I64x3, I64x3, I64x3, I64x3, c_float, c_int,
                                   c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p]),
+    "trx_attn_fwd_dropout": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_int, I64x3, c_int64, c_int64, c_int64, c_int64,
+                                     c_int64, c_int64, I64x3, I64x3, I64x3, I64x3, c_float, c_int,
+                                     c_int64, c_int64, c_int, c_float, c_uint64, c_uint32, c_void_p,
+                                     c_size_t, c_void_p]),
     "trx_attn_status": (c_int, [c_void_p, c_void_p, c_void_p]),
     "trx_attn_fwd_static_scratch": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                             c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,

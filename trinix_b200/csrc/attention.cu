@@ -70,7 +70,29 @@ struct AttnParams {
   const void* bias;
   long long bias_sb, bias_sh, bias_sq;  // elements
   int bias_kind;       // 0 none, 1 fp32, 2 the activation dtype
+  // dropout on the normalised probabilities: an element is dropped when its random byte is
+  // below drop_thr (0 = no dropout); kept ones are scaled by drop_scale = 256 / (256 - drop_thr)
+  unsigned drop_thr;
+  float drop_scale;
+  unsigned seed_lo, seed_hi, drop_offset;
 };
+
+// Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", 2011): a counter
+// based generator, so that any element's random byte can be recomputed anywhere, on the host
+// too. The dropout stream is keyed by the caller's 64-bit seed; the counter is
+// (key index / 16, query row, batch * heads + head, offset) and the 16 bytes of the result
+// belong to the 16 consecutive keys of that block, least significant byte first.
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+    c = make_uint4(hi1 ^ c.y ^ k0, lo1, hi0 ^ c.w ^ k1, lo0);
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return c;
+}
 
 // ------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -339,7 +361,8 @@ __device__ __forceinline__ TileRange tile_range(const AttnParams& p, int row0) {
   return r;
 }
 
-// BIAS: the instantiation that reads a dense additive mask; the other one carries none of it.
+// BIAS: the instantiation with the rarely used features — a dense additive mask and / or dropout,
+// each behind a run-time flag; the other instantiation carries none of it.
 template <int D, bool BF16, bool BIAS>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
     attn_fwd_kernel(const __grid_constant__ AttnParams p) {
@@ -619,7 +642,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     const float sl2 = p.scale_log2;
     const float slope2 = p.slopes ? p.slopes[h] * 1.4426950408889634f : 0.0f;
     const bool has_alibi = p.slopes != nullptr;
-    constexpr bool has_bias = BIAS;
+    const bool has_bias = BIAS && p.bias_kind != 0;
+    const bool has_drop = BIAS && p.drop_thr != 0u;
     // rows of the dense mask that this thread's two score rows read (valid rows only)
     const uint8_t* brow[2] = {nullptr, nullptr};
     if (has_bias) {
@@ -659,7 +683,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         else if (c0 >= row1) alibi_sgn = -1;          // every key at or after every query
       }
       // general path: a tile that straddles the diagonal under ALiBi, or a non-positive scale
-      const bool general = (has_alibi && alibi_sgn == 0) || !(sl2 > 0.0f) || has_bias;
+      const bool general = (has_alibi && alibi_sgn == 0) || !(sl2 > 0.0f) || has_bias || has_drop;
       float m_tile[2] = {-INFINITY, -INFINITY};
       float off[2] = {0.0f, 0.0f};  // fast path: x = t * sl2 + off
       if (general) {
@@ -787,14 +811,31 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       // 4g + q4). Slot 2g + hr never lies ahead of the scores still to be read (4g + 2hr ..).
       float2 lsum[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
       if (general) {
+        uint4 rnd[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
 #pragma unroll
         for (int g = 0; g < 16; ++g) {
 #pragma unroll
           for (int hr = 0; hr < 2; ++hr) {
-            const float p0 = fast_exp2(__uint_as_float(sr[4 * g + 2 * hr]) - m_ref[hr]);
-            const float p1 = fast_exp2(__uint_as_float(sr[4 * g + 2 * hr + 1]) - m_ref[hr]);
-            lsum[hr].x += p0;
+            float p0 = fast_exp2(__uint_as_float(sr[4 * g + 2 * hr]) - m_ref[hr]);
+            float p1 = fast_exp2(__uint_as_float(sr[4 * g + 2 * hr + 1]) - m_ref[hr]);
+            lsum[hr].x += p0;  // the normaliser sums the undropped probabilities
             lsum[hr].y += p1;
+            if (has_drop) {
+              // one generator call per 16 keys: group g (8 keys) and g + 1 share it
+              if ((g & 1) == 0)
+                rnd[hr] = philox4x32_10(
+                    make_uint4(static_cast<uint32_t>((c0 + 8 * g) >> 4),
+                               static_cast<uint32_t>(row_g[hr]),
+                               static_cast<uint32_t>(b * p.Hq + h), p.drop_offset),
+                    p.seed_lo, p.seed_hi);
+              // keys 8g + 2*q4 + {0, 1} of the tile = bytes 8(g&1) + 2*q4 + {0, 1} of the block
+              const int lc = 8 * (g & 1) + 2 * q4;
+              const uint32_t* rw = reinterpret_cast<const uint32_t*>(&rnd[hr]);
+              const uint32_t word = (lc < 4) ? rw[0] : (lc < 8) ? rw[1] : (lc < 12) ? rw[2] : rw[3];
+              const uint32_t two = word >> (8 * (lc & 3));  // lc is even: both bytes in one word
+              if ((two & 0xffu) < p.drop_thr) p0 = 0.0f;
+              if (((two >> 8) & 0xffu) < p.drop_thr) p1 = 0.0f;
+            }
             sr[2 * g + hr] = pack16<BF16>(p0, p1);
           }
         }
@@ -872,7 +913,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       const int row = row0 + r;
       const float l_row = xch[r];
       const float m_row = xch[ATT_BM + r];
-      const float inv = (n_it > 0 && l_row > 0.0f) ? __fdividef(1.0f, l_row) : 0.0f;
+      float inv = (n_it > 0 && l_row > 0.0f) ? __fdividef(1.0f, l_row) : 0.0f;
+      if (BIAS && p.drop_thr != 0u) inv *= p.drop_scale;  // kept probabilities count 1 / (1 - p)
       const uint32_t o_addr = tmem_base + (static_cast<uint32_t>(wq * 32) << 16) + 2 * ATT_BN +
                               t * ATT_BN + sub * OC;
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
@@ -1019,8 +1061,8 @@ static int launch_attn_bias(const AttnParams& p, cudaStream_t stream) {
 
 template <int D, bool BF16>
 static int launch_attn(const AttnParams& p, cudaStream_t stream) {
-  return p.bias_kind != 0 ? launch_attn_bias<D, BF16, true>(p, stream)
-                          : launch_attn_bias<D, BF16, false>(p, stream);
+  return (p.bias_kind != 0 || p.drop_thr != 0u) ? launch_attn_bias<D, BF16, true>(p, stream)
+                                                : launch_attn_bias<D, BF16, false>(p, stream);
 }
 
 }  // namespace trx
@@ -1039,8 +1081,10 @@ static int attn_fwd_prepare(AttnParams& p, bool* nothing_to_do, const void* q, c
                             const int64_t k_strides[3], const int64_t v_strides[3],
                             const int64_t o_strides[3], float scale, int causal,
                             int64_t window_left, int64_t window_right, int dtype,
-                            void* workspace, size_t workspace_bytes) {
+                            void* workspace, size_t workspace_bytes, float dropout_p = 0.0f,
+                            uint64_t seed = 0, uint32_t offset = 0) {
   *nothing_to_do = false;
+  if (!(dropout_p >= 0.0f) || !(dropout_p < 1.0f)) return TRX_ERR_SHAPE;
   if (dtype != TRX_BF16 && dtype != TRX_F16) return TRX_ERR_DTYPE;
   if (bias) {
     if (bias_dtype != TRX_F32 && bias_dtype != dtype) return TRX_ERR_DTYPE;
@@ -1117,6 +1161,16 @@ static int attn_fwd_prepare(AttnParams& p, bool* nothing_to_do, const void* q, c
     p.bias_sq = bias_strides[2];
     p.bias_kind = bias_dtype == TRX_F32 ? 1 : 2;
   }
+  if (dropout_p > 0.0f) {
+    // the drop probability is realised in steps of 1/256 (one random byte per element)
+    unsigned thr = static_cast<unsigned>(dropout_p * 256.0f + 0.5f);
+    thr = thr < 1u ? 1u : (thr > 255u ? 255u : thr);
+    p.drop_thr = thr;
+    p.drop_scale = 256.0f / static_cast<float>(256u - thr);
+    p.seed_lo = static_cast<unsigned>(seed & 0xffffffffull);
+    p.seed_hi = static_cast<unsigned>(seed >> 32);
+    p.drop_offset = offset;
+  }
   return TRX_OK;
 }
 
@@ -1133,13 +1187,15 @@ static int attn_fwd_impl(const void* q, const void* k, const void* v, void* out,
                          const int64_t q_strides[3], const int64_t k_strides[3],
                          const int64_t v_strides[3], const int64_t o_strides[3], float scale,
                          int causal, int64_t window_left, int64_t window_right, int dtype,
-                         void* workspace, size_t workspace_bytes, void* stream) {
+                         void* workspace, size_t workspace_bytes, void* stream,
+                         float dropout_p = 0.0f, uint64_t seed = 0, uint32_t offset = 0) {
   AttnParams p;
   bool nothing_to_do = false;
   const int rc = attn_fwd_prepare(p, &nothing_to_do, q, k, v, out, lse_or_null, slopes_or_null,
                                   bias, bias_dtype, bias_strides, B, Sq, Sk, Hq, Hk, D, q_strides,
                                   k_strides, v_strides, o_strides, scale, causal, window_left,
-                                  window_right, dtype, workspace, workspace_bytes);
+                                  window_right, dtype, workspace, workspace_bytes, dropout_p, seed,
+                                  offset);
   if (rc != TRX_OK || nothing_to_do) return rc;
   return attn_fwd_launch(p, D, stream);
 }
@@ -1183,6 +1239,23 @@ extern "C" int trx_attn_fwd_mask(const void* q, const void* k, const void* v, vo
   return attn_fwd_impl(q, k, v, out, lse_or_null, slopes_or_null, mask, mask_dtype, mask_strides,
                        B, Sq, Sk, Hq, Hk, D, q_strides, k_strides, v_strides, o_strides, scale,
                        causal, window_left, window_right, dtype, workspace, workspace_bytes, stream);
+}
+
+extern "C" int trx_attn_fwd_dropout(const void* q, const void* k, const void* v, void* out,
+                                    float* lse_or_null, const float* slopes_or_null,
+                                    const void* mask_or_null, int mask_dtype,
+                                    const int64_t mask_strides[3], int64_t B, int64_t Sq,
+                                    int64_t Sk, int64_t Hq, int64_t Hk, int64_t D,
+                                    const int64_t q_strides[3], const int64_t k_strides[3],
+                                    const int64_t v_strides[3], const int64_t o_strides[3],
+                                    float scale, int causal, int64_t window_left,
+                                    int64_t window_right, int dtype, float dropout_p,
+                                    uint64_t seed, uint32_t offset, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
+  return attn_fwd_impl(q, k, v, out, lse_or_null, slopes_or_null, mask_or_null, mask_dtype,
+                       mask_strides, B, Sq, Sk, Hq, Hk, D, q_strides, k_strides, v_strides,
+                       o_strides, scale, causal, window_left, window_right, dtype, workspace,
+                       workspace_bytes, stream, dropout_p, seed, offset);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -40,6 +40,7 @@ struct Pack<float> {
     f[0] = make_float2(__uint_as_float(r.x), __uint_as_float(r.y));
     f[1] = make_float2(__uint_as_float(r.z), __uint_as_float(r.w));
   }
+  __device__ __forceinline__ static void unpack2_fma(const uint4& r, float2 (&f)[2]) { unpack2(r, f); }
   // Running max of |x| over a vector; `acc` is an opaque per-thread accumulator.
   using AbsAcc = float;
   __device__ __forceinline__ static AbsAcc absacc_init() { return 0.0f; }
@@ -73,6 +74,20 @@ struct Pack<__nv_bfloat16> {
   }
   __device__ __forceinline__ static void unpack2(const uint4& r, float2 (&f)[4]) {
     f[0] = cvt2(r.x); f[1] = cvt2(r.y); f[2] = cvt2(r.z); f[3] = cvt2(r.w);
+  }
+  // The same conversion as one mixed-precision add per element (x + -0.0 in fp32: exact, keeps
+  // the sign of zero). It runs on the FMA pipe, where the shift / mask pair of cvt2 takes two
+  // slots of the half-rate integer pipe.
+  __device__ __forceinline__ static float2 cvt2_fma(uint32_t u) {
+    float lo, hi;
+    asm("{.reg .b16 l, h; mov.b32 {l, h}, %2; add.rn.f32.bf16 %0, l, 0f80000000; "
+        "add.rn.f32.bf16 %1, h, 0f80000000;}"
+        : "=f"(lo), "=f"(hi)
+        : "r"(u));
+    return make_float2(lo, hi);
+  }
+  __device__ __forceinline__ static void unpack2_fma(const uint4& r, float2 (&f)[4]) {
+    f[0] = cvt2_fma(r.x); f[1] = cvt2_fma(r.y); f[2] = cvt2_fma(r.z); f[3] = cvt2_fma(r.w);
   }
   using AbsAcc = __nv_bfloat162;
   __device__ __forceinline__ static AbsAcc absacc_init() { return __float2bfloat162_rn(0.0f); }
@@ -129,6 +144,17 @@ struct Pack<__half> {
   }
   __device__ __forceinline__ static void unpack2(const uint4& r, float2 (&f)[4]) {
     f[0] = cvt2(r.x); f[1] = cvt2(r.y); f[2] = cvt2(r.z); f[3] = cvt2(r.w);
+  }
+  __device__ __forceinline__ static float2 cvt2_fma(uint32_t u) {
+    float lo, hi;
+    asm("{.reg .b16 l, h; mov.b32 {l, h}, %2; add.rn.f32.f16 %0, l, 0f80000000; "
+        "add.rn.f32.f16 %1, h, 0f80000000;}"
+        : "=f"(lo), "=f"(hi)
+        : "r"(u));
+    return make_float2(lo, hi);
+  }
+  __device__ __forceinline__ static void unpack2_fma(const uint4& r, float2 (&f)[4]) {
+    f[0] = cvt2_fma(r.x); f[1] = cvt2_fma(r.y); f[2] = cvt2_fma(r.z); f[3] = cvt2_fma(r.w);
   }
   using AbsAcc = __half2;
   __device__ __forceinline__ static AbsAcc absacc_init() { return __float2half2_rn(0.0f); }

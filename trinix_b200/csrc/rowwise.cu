@@ -42,6 +42,13 @@ namespace trx {
 #define TRX_ROW_MIXED_SS 1
 #endif
 
+// Unpack 16-bit pairs to fp32 on the FMA pipe (one mixed-precision add per element) instead of
+// the integer pipe (shift + mask) in the encode pass of the int8 ops. Measured on the fused
+// RMSNorm -> int8 kernel at 32768 x 4096: -1.8 %; the same swap in the normalise pass costs 1.8 %.
+#ifndef TRX_QUANT_FMA_UNPACK
+#define TRX_QUANT_FMA_UNPACK 1
+#endif
+
 enum RowOp {
   OP_RMSNORM = 0,
   OP_LAYERNORM = 1,
@@ -512,7 +519,8 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
         for (int i = 0; i < VPT; ++i) {
           const int v = i * TPR + t;
           float2 f2[VEC / 2];
-          P::unpack2(raw[i], f2);
+          if constexpr (TRX_QUANT_FMA_UNPACK != 0) P::unpack2_fma(raw[i], f2);
+          else P::unpack2(raw[i], f2);
           if (live(i)) {
             uint32_t yb[VEC];
             bool exact_path = (MODE != 1);

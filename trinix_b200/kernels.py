@@ -320,8 +320,10 @@ class TritonAttentionKernel:
     Differences, all widening: k/v may have fewer heads than q (grouped / multi-query
     attention without tiling copies) and a different sequence length. `attn_mask` follows
     `_prepare_mask` (attention_kernel.py:479-495): 2-D (Sq, Sk), 3-D (B, Sq, Sk) or 4-D
-    (B, 1 | H, Sq, Sk), additive, read through its broadcast strides. `dropout_p > 0` is not
-    implemented and raises instead of silently taking another path.
+    (B, 1 | H, Sq, Sk), additive, read through its broadcast strides. `dropout_p > 0` drops
+    normalised probabilities (the order of the reference's PyTorch backend, base.py:394-397; its
+    Triton kernel lets dropped probabilities count in the normaliser, attention_kernel.py:395-406)
+    with a Philox stream whose seed comes from torch's CPU generator.
     """
 
     @staticmethod
@@ -334,12 +336,11 @@ class TritonAttentionKernel:
               scale: Optional[float] = None, dropout_p: float = 0.0,
               window_size: Optional[tuple] = None,
               alibi_slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
-        if dropout_p and dropout_p > 0.0:
-            raise NotImplementedError("trinix_b200 attention: dropout is not implemented")
         return _run(
             lambda a, b, c: ops.attention(a, b, c, causal=causal, scale=scale,
                                           window=window_size, alibi_slopes=alibi_slopes,
-                                          attn_mask=attn_mask),
+                                          attn_mask=attn_mask,
+                                          dropout_p=float(dropout_p or 0.0)),
             q, k, v)
 
 

@@ -493,14 +493,13 @@ class FastBaseAttention(nn.Module):
     def forward_attention(self, q, k, v, attn_mask=None):
         """q (B,S,H,D); k, v (B,Sk,Hkv,D) with Hkv dividing H. Returns (B,S,H,D)."""
         if self._uses_kernel(q):
-            if self.training and self.dropout > 0.0:
-                raise NotImplementedError("attention dropout is not implemented on the kernel path")
             window = None
             if self.use_sliding_window:
                 w = self.sliding_window_size
                 window = (w, 0 if self.causal else w)
             slopes = self.position_embedding.slopes if self.position_method == "alibi" else None
             return triton_attn_func(q, k, v, attn_mask=attn_mask, softmax_scale=self.scale,
+                                    dropout_p=self.dropout if self.training else 0.0,
                                     causal=self.causal, window_size=window, alibi_slopes=slopes)
         g = q.shape[2] // k.shape[2]
         if g > 1:

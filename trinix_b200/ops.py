@@ -547,6 +547,13 @@ def attention_status(device=None) -> int:
     return word
 
 
+def dropout_seed() -> int:
+    """A fresh 62-bit seed for one dropout call, drawn from torch's CPU generator: reproducible
+    under torch.manual_seed, and no device synchronisation (the reference draws its seed with
+    `.item()` on a CUDA tensor, trinix/kernels/attention_kernel.py:526-532)."""
+    return int(torch.randint(0, 2 ** 62, (1,), dtype=torch.int64).item())
+
+
 def _dense_mask(mask: torch.Tensor, B: int, Hq: int, Sq: int, Sk: int, act_dtype):
     """The mask as the kernel reads it: fp32 or the activation dtype, unit key stride, and the
     (batch, head, query) element strides of its broadcast view (shape rules of
@@ -581,13 +588,16 @@ def _dense_mask(mask: torch.Tensor, B: int, Hq: int, Sq: int, Sk: int, act_dtype
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = False,
               scale: Optional[float] = None, window: Optional[Tuple[int, int]] = None,
               alibi_slopes: Optional[torch.Tensor] = None, return_lse: bool = False,
-              attn_mask: Optional[torch.Tensor] = None):
+              attn_mask: Optional[torch.Tensor] = None, dropout_p: float = 0.0,
+              seed: Optional[int] = None, offset: int = 0):
     """softmax(scale * q k^T + bias) v; q (B,Sq,Hq,D), k/v (B,Sk,Hk,D), Hq % Hk == 0.
 
     Query head h reads kv head h // (Hq // Hk). window = (left, right) keeps keys with
     -left <= j - i <= right. alibi_slopes (Hq,) adds -slope * |i - j|. attn_mask is a dense
     additive mask (Sq,Sk), (B,Sq,Sk), (B,1,Sq,Sk) or (B,Hq,Sq,Sk), float (added to the scaled
-    scores) or bool (True = hidden), broadcast by stride, never expanded.
+    scores) or bool (True = hidden), broadcast by stride, never expanded. dropout_p in [0, 1)
+    drops normalised probabilities (realised in steps of 1/256) with a Philox stream keyed by
+    `seed` (drawn from torch's CPU generator when None) and `offset`; see dropout_seed().
     """
     dev = _need_cuda(q, k, v, alibi_slopes, attn_mask)
     if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.bfloat16, torch.float16):
@@ -616,6 +626,26 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
     ws = _workspace(dev)
     # a failure recorded by an earlier launch surfaces here, before more work is queued
     _raise_if_failed("trx_attn_fwd", dev)
+    if dropout_p:
+        if not 0.0 <= dropout_p < 1.0:
+            raise ValueError(f"dropout_p must be in [0, 1), got {dropout_p}")
+        if seed is None:
+            seed = dropout_seed()
+        m, mstr = (None, (0, 0, Sk))
+        if attn_mask is not None:
+            m, mstr = _dense_mask(attn_mask, B, Hq, Sq, Sk, q.dtype)
+        with torch.cuda.device(dev):
+            rc = _lib.load().trx_attn_fwd_dropout(
+                _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(lse), _ptr(slopes), _ptr(m),
+                _code(m) if m is not None else 0, I64x3(*mstr), B, Sq, Sk, Hq, Hk, D,
+                I64x3(*q.stride()[:3]), I64x3(*k.stride()[:3]), I64x3(*v.stride()[:3]),
+                I64x3(*out.stride()[:3]), float(scale), int(bool(causal)), wl, wr, _code(q),
+                float(dropout_p), int(seed) & (2 ** 64 - 1), int(offset) & 0xFFFFFFFF, _ptr(ws),
+                ws.numel(), _stream(dev))
+            _lib.check("trx_attn_fwd_dropout", rc)
+            _queue_status_copy(ws, dev)
+        _count()
+        return (out, lse) if return_lse else out
     if attn_mask is not None:
         m, mstr = _dense_mask(attn_mask, B, Hq, Sq, Sk, q.dtype)
         with torch.cuda.device(dev):
