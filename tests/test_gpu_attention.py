@@ -133,12 +133,33 @@ def test_lse_output(cuda):
     torch.testing.assert_close(lse.cpu(), torch.logsumexp(s, -1), rtol=1e-3, atol=1e-3)
 
 
-def test_golden_core_vectors_d32_rejected_cleanly(cuda):
-    """head_dim 32 (the golden attention vectors) is outside this build: a clear error, no
-    fallback."""
-    q = G("attn_q").bfloat16().to(cuda)
-    with pytest.raises(T._lib.TrinixB200Error) as e:
-        T.triton_attn_func(q, q, q)
+def test_golden_attention_vectors_from_the_reference(cuda):
+    """The attention outputs the unmodified reference produced (its PyTorch backend, fp32 and
+    bf16, head dim 32, GQA 4:2, causal / not / causal + ALiBi): the kernel meets them directly.
+    Head dim 32 runs as 64 with zero columns appended."""
+    q, k, v = (G(n).bfloat16().to(cuda) for n in ("attn_q", "attn_k", "attn_v"))
+    for causal in (False, True):
+        out = T.triton_attn_func(q, k, v, causal=causal)
+        assert out.shape == q.shape
+        want_bf16 = G(f"attn_out_bf16_causal{int(causal)}").float()
+        want_f32 = G(f"attn_out_causal{int(causal)}")     # from the fp32 inputs
+        assert float((out.float().cpu() - want_bf16).abs().max()) <= TOL
+        assert float((out.float().cpu() - want_f32).abs().max()) <= 2 * TOL  # + input rounding
+    out = T.triton_attn_func(q, k, v, causal=True, alibi_slopes=R.alibi_slopes_ref(4).to(cuda))
+    assert float((out.float().cpu() - G("attn_out_alibi")).abs().max()) <= 2 * TOL
+    assert T.attention_status(cuda) == 0
+    # head dims between the two built ones, and the one beyond them
+    g = torch.Generator().manual_seed(3)
+    q96 = torch.randn(1, 200, 4, 96, generator=g).bfloat16()
+    k96 = torch.randn(1, 200, 2, 96, generator=g).bfloat16()
+    v96 = torch.randn(1, 200, 2, 96, generator=g).bfloat16()
+    out96, lse96 = T.attention(q96.to(cuda), k96.to(cuda), v96.to(cuda), causal=True, return_lse=True)
+    ref96 = R.attention_variant_ref(q96.float(), k96.float(), v96.float(), None, True)
+    assert out96.shape == q96.shape and lse96.shape == (1, 4, 200)
+    assert float((out96.float().cpu() - ref96).abs().max()) <= TOL
+    q256 = torch.zeros(1, 128, 2, 256, dtype=torch.bfloat16, device=cuda)
+    with pytest.raises(T._lib.TrinixB200Error) as e:     # a clear error, no fallback
+        T.triton_attn_func(q256, q256, q256)
     assert e.value.code == -6
 
 

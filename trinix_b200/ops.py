@@ -602,6 +602,21 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
     dev = _need_cuda(q, k, v, alibi_slopes, attn_mask)
     if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.bfloat16, torch.float16):
         raise TypeError("attention needs q, k, v of one dtype, bfloat16 or float16")
+    if q.dim() == 4 and q.shape[-1] not in (64, 128) and 0 < q.shape[-1] < 128:
+        # The kernel is built for head dims 64 and 128. Any smaller one runs as the next of the
+        # two with zero columns appended: they add nothing to q.k and produce output columns that
+        # are cut off again. Costs one padded copy of q, k, v; the scale keeps the true head dim.
+        d_true = q.shape[-1]
+        d_pad = 64 if d_true < 64 else 128
+        if scale is None:
+            scale = d_true ** -0.5
+        pad = lambda t: torch.nn.functional.pad(t, (0, d_pad - d_true))
+        res = attention(pad(q), pad(k), pad(v), causal=causal, scale=scale, window=window,
+                        alibi_slopes=alibi_slopes, return_lse=return_lse, attn_mask=attn_mask,
+                        dropout_p=dropout_p, seed=seed, offset=offset)
+        if return_lse:
+            return res[0][..., :d_true].contiguous(), res[1]
+        return res[..., :d_true].contiguous()
     q, k, v = _tma_view(q), _tma_view(k), _tma_view(v)
     B, Sq, Hq, D = q.shape
     Bk, Sk, Hk, Dk = k.shape
