@@ -43,10 +43,20 @@ namespace trx {
 #endif
 
 // Unpack 16-bit pairs to fp32 on the FMA pipe (one mixed-precision add per element) instead of
-// the integer pipe (shift + mask) in the encode pass of the int8 ops. Measured on the fused
-// RMSNorm -> int8 kernel at 32768 x 4096: -1.8 %; the same swap in the normalise pass costs 1.8 %.
+// the integer pipe (shift + mask) in the int8 ops. Measured on the fused RMSNorm -> int8 kernel
+// at 32768 x 4096, 10 CTAs per SM: -1.8 % in the encode pass, +1.8 % in the normalise pass; at
+// 16 CTAs per SM, where the ALU pipe is the busiest (59 % against 49 % FMA), the normalise pass
+// gains another 1.2 % (69.2 -> 68.4 us), so both passes use it.
 #ifndef TRX_QUANT_FMA_UNPACK
 #define TRX_QUANT_FMA_UNPACK 1
+#endif
+
+// Resident threads per SM asked for the int8 encoders in the 64-thread x 8-vector configuration
+// (caps the registers per thread at 64). These kernels are bound by the supply of eligible warps,
+// not by a pipe or by DRAM: measured on the fused RMSNorm -> int8 kernel at 32768 x 4096, 640
+// threads (96 registers) 76.6 us, 768: 72.1, 896: 70.9, 960 / 1024: 69.4, 1088: 74.5, 1280: 81.3.
+#ifndef TRX_ROW64_THREADS_PER_SM
+#define TRX_ROW64_THREADS_PER_SM 1024
 #endif
 
 enum RowOp {
@@ -76,7 +86,9 @@ __host__ __device__ constexpr int row_min_blocks(int op, int tpr, int vpt) {
   if (tpr <= 32) return 3;                      // 256-thread CTAs, 8 rows each
   if (tpr > 256) return 1;
   if (op_has_res(op)) return 768 / tpr;         // two streams + fp32 copies: more registers
-  if (tpr == 64 && vpt == 8) return 640 / tpr;  // 8 vectors per thread in flight
+  if (tpr == 64 && vpt == 8)  // 8 vectors per thread in flight
+    return (op_has_quant(op) ? TRX_ROW64_THREADS_PER_SM : 640) / tpr;
+
   return 1024 / tpr;
 }
 
@@ -453,7 +465,9 @@ __global__ void __launch_bounds__((TPR > 32 ? TPR : 256), row_min_blocks(OP, TPR
 #pragma unroll
                   for (int j = 0; j < 4; ++j) f2[j] = xf[i][j];
                 } else {
-                  P::unpack2(raw[i], f2);
+                  // the int8 forms run with the ALU pipe as their busiest: unpack on the FMA pipe
+                  if constexpr (NORM_TO_REGS && TRX_QUANT_FMA_UNPACK != 0) P::unpack2_fma(raw[i], f2);
+                  else P::unpack2(raw[i], f2);
                 }
                 uint32_t yu[4];
 #pragma unroll
