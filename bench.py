@@ -50,6 +50,7 @@ WORKLOAD = ("int8_quant: quantize+dequantize bf16[8192,4096] (0.1% outliers x20)
             "RMSNorm(4096)->int8 on bf16[16,2048,4096]; this batch per GPU")
 EST_PASS_MS = 0.12      # used only to size passes_per_step; the measured time is what is reported
 TARGET_REGION_S = 0.8
+E2E_REPEATS = 3         # end-to-end regions timed per mode; the median is reported
 
 
 def config_block(world: int) -> dict:
@@ -872,9 +873,15 @@ def main():
     # ---- end to end: pinned host buffers, copies inside the timed region -----------------------
     e2e = E2E(device, w, 99 + rank)
     e2e_passes = max(3, min(args.steps, 10))
-    modes = {}
+    # Each mode is timed E2E_REPEATS times and the median kept: one repeat can catch the caching
+    # allocator growing its pool (a synchronising cudaMalloc) or a neighbour on the host's PCIe
+    # root, which says nothing about the schedule itself. All repeats are reported.
+    modes, full_runs = {}, []
     for mode in ("full", "copies", "h2d", "d2h"):
-        modes[mode] = e2e.timed(mode, e2e_passes, sync_all)
+        runs = sorted(e2e.timed(mode, e2e_passes, sync_all) for _ in range(E2E_REPEATS))
+        modes[mode] = runs[len(runs) // 2]
+        if mode == "full":
+            full_runs = runs
     m_full, m_copies, m_h2d, m_d2h = sharding.max_over_ranks(
         [modes["full"], modes["copies"], modes["h2d"], modes["d2h"]], device)
     e2e_value = world * BYTES_PASS * e2e_passes / m_full / 1e6
@@ -913,7 +920,11 @@ def main():
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": e2e.h2d,
                     "d2h_bytes_per_step": e2e.d2h, "passes": e2e_passes,
-                    "note": "one e2e step = one pass; algorithmic bytes of the pass / wall time",
+                    "repeats": E2E_REPEATS,
+                    "repeat_values_this_rank": [
+                        round(BYTES_PASS * e2e_passes / m / 1e6, 2) for m in full_runs],
+                    "note": "one e2e step = one pass; algorithmic bytes of the pass / wall time; "
+                            "median of the repeats, max over ranks",
                     "copy_only": {
                         "value": round(world * BYTES_PASS * e2e_passes / m_copies / 1e6, 2),
                         "unit": "GB/s", "note": "same chunk schedule, kernels left out",
