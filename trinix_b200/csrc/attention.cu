@@ -209,6 +209,18 @@ __device__ __forceinline__ void mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uin
       : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]; `acc` = 0 overwrites D
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
   if constexpr (BF16) return Pack<__nv_bfloat16>::pack2(lo, hi);
@@ -504,93 +516,97 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     if (lane == 0 && JHI > JLO) {
       const uint32_t idesc_qk = make_idesc(BF16 ? 1 : 0, ATT_BM, ATT_BN, 0, 0);
       const uint32_t idesc_pv = make_idesc(BF16 ? 1 : 0, ATT_BM, D, 0, 1);
-      bool ok = true;
-      bool q_ready[ATT_NQ] = {false, false};
-      int it[ATT_NQ] = {0, 0};  // softmax iterations issued per Q tile
-      auto active = [&](int t, int j) { return j >= rng[t].jlo && j < rng[t].jhi; };
-      auto kv_wait = [&](int fill) {
-        return mbar_wait(bar(B_KVFULL + fill % ATT_STAGES), (fill / ATT_STAGES) & 1, abort_flag,
-                         p.status, ATT_ST_MMA);
-      };
+      static_assert((ATT_STAGES & (ATT_STAGES - 1)) == 0, "ring depth must be a power of two");
+      // This thread sits between the softmax warps and the tensor pipe: every cycle it spends
+      // between two groups of MMAs is a cycle the pipe idles once its short queue has drained
+      // (the same 32 MMAs per KV tile issued from a loop with per-tile state in arrays, lambdas
+      // and modulo arithmetic ran at 1.40 PFLOP/s with nothing to wait for; from straight-line
+      // code on scalars at 1.83). So: scalars only, one flat loop, both K/V waits up front.
+      const int jlo0 = rng[0].jlo, jhi0 = rng[0].jhi, jlo1 = rng[1].jlo, jhi1 = rng[1].jhi;
       // Descriptors differ only in their 14-bit start-address field (address >> 4), which is
       // the low part of the low word: build the constant part once and add offsets with one
-      // 32-bit add per operand, so that the issuing thread keeps ahead of the tensor pipe.
-      const uint64_t desc_k_major = make_desc(0, 16, 1024);            // K-major, SBO 1 KB
+      // 32-bit add per operand.
+      const uint64_t desc_k_major = make_desc(0, 16, 1024);               // K-major, SBO 1 KB
       const uint64_t desc_mn_major = make_desc(0, L::CHUNK_BYTES, 1024);  // MN-major V
       const uint32_t dk_hi = static_cast<uint32_t>(desc_k_major >> 32);
-      const uint32_t dk_lo = static_cast<uint32_t>(desc_k_major);
       const uint32_t dv_hi = static_cast<uint32_t>(desc_mn_major >> 32);
-      const uint32_t dv_lo = static_cast<uint32_t>(desc_mn_major);
+      constexpr uint32_t T16 = L::TILE_BYTES >> 4;
+      const uint32_t q_lo = static_cast<uint32_t>(desc_k_major) + ((sbase + L::Q_OFF) >> 4);
+      const uint32_t k_lo = static_cast<uint32_t>(desc_k_major) + ((sbase + L::KV_OFF) >> 4);
+      const uint32_t v_lo = static_cast<uint32_t>(desc_mn_major) + ((sbase + L::KV_OFF) >> 4);
       auto desc_of = [](uint32_t lo, uint32_t hi) {
         return (static_cast<uint64_t>(hi) << 32) | lo;
       };
-      const uint32_t q_lo0 = dk_lo + ((sbase + L::Q_OFF) >> 4);
-      const uint32_t kv_lo0 = (sbase + L::KV_OFF) >> 4;
-      auto issue_qk = [&](int t, int fill) {
-        if (!q_ready[t]) {
-          if (!mbar_wait(bar(B_QFULL + t), 0, abort_flag, p.status, ATT_ST_MMA)) return false;
-          q_ready[t] = true;
-        }
+      auto wait = [&](int b, uint32_t parity) {
+        return mbar_wait(bar(b), parity, abort_flag, p.status, ATT_ST_MMA);
+      };
+      bool ok = true;
+      if (jhi0 > jlo0) ok = wait(B_QFULL + 0, 0);
+      if (ok && jhi1 > jlo1) ok = wait(B_QFULL + 1, 0);
+      uint32_t ppar0 = 0, ppar1 = 0;  // parity of the next P hand-over per Q tile
+
+      // O_t += P_t V (P from TMEM, V MN-major from ring stage `vst`); `acc` = 0 clears O first
+      auto pv = [&](int t, uint32_t vst, uint32_t acc) {
         tc_fence_after();
-        const uint32_t qlo = q_lo0 + t * (L::TILE_BYTES >> 4);
-        const uint32_t klo = dk_lo + kv_lo0 + (fill % ATT_STAGES) * (L::TILE_BYTES >> 4);
+        const uint32_t d_tmem = tmem_base + 2 * ATT_BN + t * ATT_BN;
+        const uint32_t a_tmem = tmem_base + t * ATT_BN;
+#pragma unroll
+        for (int kk = 0; kk < ATT_BN / 16; ++kk)
+          mma_ts(d_tmem, a_tmem + kk * 8, desc_of(vst + kk * (2048 >> 4), dv_hi), idesc_pv,
+                 kk == 0 ? acc : 1u);
+      };
+      // S_t = Q_t K^T (both operands K-major in shared memory), then announce S_t
+      auto qk = [&](int t, uint32_t kst) {
+        tc_fence_after();
+        const uint32_t qst = q_lo + t * T16;
         const uint32_t d_tmem = tmem_base + t * ATT_BN;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = ((kk / 4) * L::CHUNK_BYTES + (kk % 4) * 32) >> 4;
           if (kk == 0)
-            mma_ss_first(d_tmem, desc_of(qlo + off, dk_hi), desc_of(klo + off, dk_hi), idesc_qk);
+            mma_ss_first(d_tmem, desc_of(qst + off, dk_hi), desc_of(kst + off, dk_hi), idesc_qk);
           else
-            mma_ss_acc(d_tmem, desc_of(qlo + off, dk_hi), desc_of(klo + off, dk_hi), idesc_qk);
+            mma_ss_acc(d_tmem, desc_of(qst + off, dk_hi), desc_of(kst + off, dk_hi), idesc_qk);
         }
         tc_commit(bar(B_SFULL + t));
-        return true;
-      };
-      auto issue_pv = [&](int t, int fill, bool accumulate) {
-        if (!mbar_wait(bar(B_PFULL + t), it[t] & 1, abort_flag, p.status, ATT_ST_MMA))
-          return false;
-        tc_fence_after();
-        const uint32_t vlo = dv_lo + kv_lo0 + (fill % ATT_STAGES) * (L::TILE_BYTES >> 4);
-        const uint32_t d_tmem = tmem_base + 2 * ATT_BN + t * ATT_BN;
-        const uint32_t a_tmem = tmem_base + t * ATT_BN;
-#pragma unroll
-        for (int kk = 0; kk < ATT_BN / 16; ++kk) {
-          const uint64_t vd = desc_of(vlo + kk * (2048 >> 4), dv_hi);
-          if (kk == 0 && !accumulate)
-            mma_ts_first(d_tmem, a_tmem + kk * 8, vd, idesc_pv);
-          else
-            mma_ts_acc(d_tmem, a_tmem + kk * 8, vd, idesc_pv);
-        }
-        tc_commit(bar(B_ODONE + t));
-        ++it[t];
-        return true;
       };
 
-      // prologue: S(JLO)
-      ok = kv_wait(0);
-      for (int t = 0; t < ATT_NQ && ok; ++t)
-        if (active(t, JLO)) ok = issue_qk(t, 0);
-      if (ok) tc_commit(bar(B_KVEMPTY + 0));
-      for (int j = JLO; j < JHI && ok; ++j) {
-        const int fill_v = 2 * (j - JLO) + 1;
-        const int fill_kn = fill_v + 1;
-        ok = kv_wait(fill_v);
-        bool kn_waited = false;
-        for (int t = 0; t < ATT_NQ && ok; ++t) {
-          if (active(t, j)) ok = issue_pv(t, fill_v, j > rng[t].jlo);
-          if (ok && j + 1 < JHI && active(t, j + 1)) {
-            if (!kn_waited) {
-              ok = kv_wait(fill_kn);
-              kn_waited = true;
-            }
-            if (ok) ok = issue_qk(t, fill_kn);
+      // The O accumulator is announced once, after the last P V of a Q tile: before that the
+      // softmax warps learn of a finished P V from the next S (its commit covers everything
+      // issued earlier), so the rescale of O needs no barrier of its own.
+      // Round j issues P V of KV tile j and Q K^T of tile j + 1 for each Q tile that has them;
+      // the first round (j = JLO - 1) is the prologue, S(JLO) alone. Ring fills: K(j) is fill
+      // 2 (j - JLO), V(j) the one after.
+#pragma unroll 1
+      for (int j = JLO - 1; j < JHI && ok; ++j) {
+        const int f = 2 * (j - JLO);
+        const bool has_pv = j >= JLO, has_qk = j + 1 < JHI;
+        const uint32_t fv = static_cast<uint32_t>(f + 1), fk = static_cast<uint32_t>(f + 2);
+        const uint32_t sv = fv & (ATT_STAGES - 1), sk = fk & (ATT_STAGES - 1);
+        if (has_pv) ok = wait(B_KVFULL + sv, (fv / ATT_STAGES) & 1);
+        if (ok && has_qk) ok = wait(B_KVFULL + sk, (fk / ATT_STAGES) & 1);
+        const uint32_t vst = v_lo + sv * T16, kst = k_lo + sk * T16;
+        if (ok && has_pv && j >= jlo0 && j < jhi0) {
+          ok = wait(B_PFULL + 0, ppar0);
+          ppar0 ^= 1u;
+          if (ok) {
+            pv(0, vst, j > jlo0 ? 1u : 0u);
+            if (j == jhi0 - 1) tc_commit(bar(B_ODONE + 0));
           }
         }
-        if (!ok) break;
-        tc_commit(bar(B_KVEMPTY + fill_v % ATT_STAGES));
-        if (j + 1 < JHI) {
-          if (!kn_waited) ok = kv_wait(fill_kn);
-          if (ok) tc_commit(bar(B_KVEMPTY + fill_kn % ATT_STAGES));
+        if (ok && has_qk && j + 1 >= jlo0 && j + 1 < jhi0) qk(0, kst);
+        if (ok && has_pv && j >= jlo1 && j < jhi1) {
+          ok = wait(B_PFULL + 1, ppar1);
+          ppar1 ^= 1u;
+          if (ok) {
+            pv(1, vst, j > jlo1 ? 1u : 0u);
+            if (j == jhi1 - 1) tc_commit(bar(B_ODONE + 1));
+          }
+        }
+        if (ok && has_qk && j + 1 >= jlo1 && j + 1 < jhi1) qk(1, kst);
+        if (ok) {
+          if (has_pv) tc_commit(bar(B_KVEMPTY + sv));
+          if (has_qk) tc_commit(bar(B_KVEMPTY + sk));
         }
       }
       if (!ok) {
@@ -860,12 +876,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       l_run[1] += lsum[1].x + lsum[1].y;
       tmem_st_16x128b_x16(s_addr, sr);
 
-      // O rescale (rare after the first tiles): needs the previous PV of this tile done
+      // O rescale (rare after the first tiles): needs the previous P V of this tile done, which
+      // the S of this iteration implies (its commit was issued after that P V)
       if (__any_sync(0xffffffffu, rescale)) {
-        ok = __all_sync(0xffffffffu, mbar_wait(bar(B_ODONE + t), (itn - 1) & 1, abort_flag,
-                                               p.status, ATT_ST_SOFTMAX));
-        if (ok) {
-          tc_fence_after();
+        {
           uint32_t orr[D / 2];  // same fragment layout as the scores
           if constexpr (D == 128) tmem_ld_16x256b_x16(o_addr16, orr);
           else tmem_ld_16x256b_x8(o_addr16, orr);
@@ -902,8 +916,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                       mbar_wait(bar(B_XCH + t), 0, abort_flag, p.status, ATT_ST_SOFTMAX));
     }
     if (ok && n_it > 0) {
-      ok = __all_sync(0xffffffffu, mbar_wait(bar(B_ODONE + t), (n_it - 1) & 1, abort_flag,
-                                             p.status, ATT_ST_SOFTMAX));
+      ok = __all_sync(0xffffffffu,
+                      mbar_wait(bar(B_ODONE + t), 0, abort_flag, p.status, ATT_ST_SOFTMAX));
       tc_fence_after();
     }
     if (ok) {
