@@ -9,7 +9,8 @@
 //   warp  16    TMA producer: Q once, then K and V tiles through a 4-stage shared-memory ring
 //               (cp.async.bulk.tensor, 128-byte swizzle, no multicast)
 //   warp  17    MMA issuer: tcgen05.mma kind::f16, S = Q K^T (both operands from shared memory)
-//               and O += P V (P read from TMEM, V from shared memory, MN-major)
+//               and O += P V (P read from TMEM, V from shared memory, MN-major); one thread,
+//               flat scalar code, specialised for the rounds in which both Q tiles are active
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each; P (16-bit) overwrites the
 // first 64 columns of its S. The softmax groups read S with tcgen05.ld, exponentiate with
 // exp2 (scale*log2e folded into one FMA, ALiBi as one more), write P back with tcgen05.st,
@@ -25,6 +26,7 @@
 
 #include <atomic>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -187,28 +189,6 @@ __device__ __forceinline__ void mma_ss_acc(uint32_t d_tmem, uint64_t a_desc, uin
       : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc)
       : "memory");
 }
-// D[tmem] = A[tmem] * B[smem]  (first) / D[tmem] += A[tmem] * B[smem]  (acc)
-__device__ __forceinline__ void mma_ts_first(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                             uint32_t idesc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, 0, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      :
-      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
-      : "memory");
-}
-__device__ __forceinline__ void mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                           uint32_t idesc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.eq.b32 p, 0, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      :
-      : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
-      : "memory");
-}
-
 // D[tmem] (+)= A[tmem] * B[smem]; `acc` = 0 overwrites D
 __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
                                        uint32_t idesc, uint32_t acc) {
@@ -577,38 +557,49 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       // Round j issues P V of KV tile j and Q K^T of tile j + 1 for each Q tile that has them;
       // the first round (j = JLO - 1) is the prologue, S(JLO) alone. Ring fills: K(j) is fill
       // 2 (j - JLO), V(j) the one after.
-#pragma unroll 1
-      for (int j = JLO - 1; j < JHI && ok; ++j) {
+      // `STEADY` rounds (both Q tiles have this KV tile and the next, neither is at its first):
+      // every test below is a compile-time constant and what is left is waits, MMAs, commits.
+      auto round = [&](int j, auto steady_tag) {
+        constexpr bool STEADY = decltype(steady_tag)::value;
         const int f = 2 * (j - JLO);
-        const bool has_pv = j >= JLO, has_qk = j + 1 < JHI;
+        const bool has_pv = STEADY || j >= JLO, has_qk = STEADY || j + 1 < JHI;
         const uint32_t fv = static_cast<uint32_t>(f + 1), fk = static_cast<uint32_t>(f + 2);
         const uint32_t sv = fv & (ATT_STAGES - 1), sk = fk & (ATT_STAGES - 1);
         if (has_pv) ok = wait(B_KVFULL + sv, (fv / ATT_STAGES) & 1);
         if (ok && has_qk) ok = wait(B_KVFULL + sk, (fk / ATT_STAGES) & 1);
         const uint32_t vst = v_lo + sv * T16, kst = k_lo + sk * T16;
-        if (ok && has_pv && j >= jlo0 && j < jhi0) {
+        if (ok && (STEADY || (has_pv && j >= jlo0 && j < jhi0))) {
           ok = wait(B_PFULL + 0, ppar0);
           ppar0 ^= 1u;
           if (ok) {
-            pv(0, vst, j > jlo0 ? 1u : 0u);
-            if (j == jhi0 - 1) tc_commit(bar(B_ODONE + 0));
+            pv(0, vst, (STEADY || j > jlo0) ? 1u : 0u);
+            if (!STEADY && j == jhi0 - 1) tc_commit(bar(B_ODONE + 0));
           }
         }
-        if (ok && has_qk && j + 1 >= jlo0 && j + 1 < jhi0) qk(0, kst);
-        if (ok && has_pv && j >= jlo1 && j < jhi1) {
+        if (ok && (STEADY || (has_qk && j + 1 >= jlo0 && j + 1 < jhi0))) qk(0, kst);
+        if (ok && (STEADY || (has_pv && j >= jlo1 && j < jhi1))) {
           ok = wait(B_PFULL + 1, ppar1);
           ppar1 ^= 1u;
           if (ok) {
-            pv(1, vst, j > jlo1 ? 1u : 0u);
-            if (j == jhi1 - 1) tc_commit(bar(B_ODONE + 1));
+            pv(1, vst, (STEADY || j > jlo1) ? 1u : 0u);
+            if (!STEADY && j == jhi1 - 1) tc_commit(bar(B_ODONE + 1));
           }
         }
-        if (ok && has_qk && j + 1 >= jlo1 && j + 1 < jhi1) qk(1, kst);
+        if (ok && (STEADY || (has_qk && j + 1 >= jlo1 && j + 1 < jhi1))) qk(1, kst);
         if (ok) {
           if (has_pv) tc_commit(bar(B_KVEMPTY + sv));
           if (has_qk) tc_commit(bar(B_KVEMPTY + sk));
         }
-      }
+      };
+      // steady rounds: max(jlo) < j and j + 1 < min(jhi)
+      const int js = max(jlo0, jlo1) + 1, je = min(jhi0, jhi1) - 1;
+      int j = JLO - 1;
+#pragma unroll 1
+      for (; j < JHI && j < js && ok; ++j) round(j, std::false_type{});
+#pragma unroll 1
+      for (; j < je && ok; ++j) round(j, std::true_type{});
+#pragma unroll 1
+      for (; j < JHI && ok; ++j) round(j, std::false_type{});
       if (!ok) {
         // drain whatever was issued before giving up
         tc_commit(bar(B_DRAIN));
