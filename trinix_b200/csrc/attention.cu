@@ -68,6 +68,7 @@ struct AttnParams {
   int win_left, win_right;  // < 0: no window
   int is_bf16;
   int reverse_m;       // schedule the heaviest (last) row blocks first
+  int reverse_kv;      // visit a row block's KV tiles from the last to the first
   // dense additive mask (B, Hq, Sq, Sk) with unit key stride; batch / head strides may be 0
   const void* bias;
   long long bias_sb, bias_sh, bias_sq;  // elements
@@ -405,7 +406,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   // One K or V tile into ring stage fill % STAGES (K and V tiles alternate: even fills are K).
   auto issue_fill = [&](int fill) {
     const int s = fill % ATT_STAGES;
-    const int j = JLO + fill / 2;
+    const int j = p.reverse_kv ? JHI - 1 - fill / 2 : JLO + fill / 2;
     const bool is_k = (fill & 1) == 0;
     mbar_expect_tx(bar(B_KVFULL + s), L::TILE_BYTES);
     fills_issued[s] = fill / ATT_STAGES + 1;
@@ -557,49 +558,60 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       // Round j issues P V of KV tile j and Q K^T of tile j + 1 for each Q tile that has them;
       // the first round (j = JLO - 1) is the prologue, S(JLO) alone. Ring fills: K(j) is fill
       // 2 (j - JLO), V(j) the one after.
-      // `STEADY` rounds (both Q tiles have this KV tile and the next, neither is at its first):
-      // every test below is a compile-time constant and what is left is waits, MMAs, commits.
-      auto round = [&](int j, auto steady_tag) {
+      // Round r (-1 .. n - 1) issues P V of the r-th visited KV tile and Q K^T of the next one;
+      // the visiting order is ascending or descending (reverse_kv). `STEADY` rounds (both Q
+      // tiles have this KV tile and the next, neither is at its first): every test below is a
+      // compile-time constant and what is left is waits, MMAs, commits.
+      const int n_rounds = JHI - JLO;
+      const bool rev = p.reverse_kv != 0;
+      const int first0 = rev ? jhi0 - 1 : jlo0, last0 = rev ? jlo0 : jhi0 - 1;
+      const int first1 = rev ? jhi1 - 1 : jlo1, last1 = rev ? jlo1 : jhi1 - 1;
+      auto round = [&](int r, auto steady_tag) {
         constexpr bool STEADY = decltype(steady_tag)::value;
-        const int f = 2 * (j - JLO);
-        const bool has_pv = STEADY || j >= JLO, has_qk = STEADY || j + 1 < JHI;
+        const int f = 2 * r;  // ring fills: K of visit r is fill 2r, V the one after
+        const bool has_pv = STEADY || r >= 0, has_qk = STEADY || r + 1 < n_rounds;
+        const int jp = rev ? JHI - 1 - r : JLO + r;  // KV tile of the P V
+        const int jq = rev ? jp - 1 : jp + 1;        // KV tile of the next Q K^T
         const uint32_t fv = static_cast<uint32_t>(f + 1), fk = static_cast<uint32_t>(f + 2);
         const uint32_t sv = fv & (ATT_STAGES - 1), sk = fk & (ATT_STAGES - 1);
         if (has_pv) ok = wait(B_KVFULL + sv, (fv / ATT_STAGES) & 1);
         if (ok && has_qk) ok = wait(B_KVFULL + sk, (fk / ATT_STAGES) & 1);
         const uint32_t vst = v_lo + sv * T16, kst = k_lo + sk * T16;
-        if (ok && (STEADY || (has_pv && j >= jlo0 && j < jhi0))) {
+        if (ok && (STEADY || (has_pv && jp >= jlo0 && jp < jhi0))) {
           ok = wait(B_PFULL + 0, ppar0);
           ppar0 ^= 1u;
           if (ok) {
-            pv(0, vst, (STEADY || j > jlo0) ? 1u : 0u);
-            if (!STEADY && j == jhi0 - 1) tc_commit(bar(B_ODONE + 0));
+            pv(0, vst, (STEADY || jp != first0) ? 1u : 0u);
+            if (!STEADY && jp == last0) tc_commit(bar(B_ODONE + 0));
           }
         }
-        if (ok && (STEADY || (has_qk && j + 1 >= jlo0 && j + 1 < jhi0))) qk(0, kst);
-        if (ok && (STEADY || (has_pv && j >= jlo1 && j < jhi1))) {
+        if (ok && (STEADY || (has_qk && jq >= jlo0 && jq < jhi0))) qk(0, kst);
+        if (ok && (STEADY || (has_pv && jp >= jlo1 && jp < jhi1))) {
           ok = wait(B_PFULL + 1, ppar1);
           ppar1 ^= 1u;
           if (ok) {
-            pv(1, vst, (STEADY || j > jlo1) ? 1u : 0u);
-            if (!STEADY && j == jhi1 - 1) tc_commit(bar(B_ODONE + 1));
+            pv(1, vst, (STEADY || jp != first1) ? 1u : 0u);
+            if (!STEADY && jp == last1) tc_commit(bar(B_ODONE + 1));
           }
         }
-        if (ok && (STEADY || (has_qk && j + 1 >= jlo1 && j + 1 < jhi1))) qk(1, kst);
+        if (ok && (STEADY || (has_qk && jq >= jlo1 && jq < jhi1))) qk(1, kst);
         if (ok) {
           if (has_pv) tc_commit(bar(B_KVEMPTY + sv));
           if (has_qk) tc_commit(bar(B_KVEMPTY + sk));
         }
       };
-      // steady rounds: max(jlo) < j and j + 1 < min(jhi)
-      const int js = max(jlo0, jlo1) + 1, je = min(jhi0, jhi1) - 1;
-      int j = JLO - 1;
+      // steady rounds: the P V tile lies in (max(jlo), min(jhi) - 1) and is not a Q tile's first
+      // or last, the next tile is inside both ranges
+      const int lo_s = max(jlo0, jlo1) + 1, hi_s = min(jhi0, jhi1) - 2;  // jp in [lo_s, hi_s]
+      const int rs = rev ? JHI - 1 - hi_s : lo_s - JLO;                  // first steady round
+      const int re = rev ? JHI - 1 - lo_s + 1 : hi_s - JLO + 1;          // one past the last
+      int r = -1;
 #pragma unroll 1
-      for (; j < JHI && j < js && ok; ++j) round(j, std::false_type{});
+      for (; r < n_rounds && r < rs && ok; ++r) round(r, std::false_type{});
 #pragma unroll 1
-      for (; j < je && ok; ++j) round(j, std::true_type{});
+      for (; r < re && ok; ++r) round(r, std::true_type{});
 #pragma unroll 1
-      for (; j < JHI && ok; ++j) round(j, std::false_type{});
+      for (; r < n_rounds && ok; ++r) round(r, std::false_type{});
       if (!ok) {
         // drain whatever was issued before giving up
         tc_commit(bar(B_DRAIN));
@@ -668,7 +680,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     bool ok = true;
 
     for (int itn = 0; itn < n_it && ok; ++itn) {
-      const int j = rng[t].jlo + itn;
+      const int j = p.reverse_kv ? rng[t].jhi - 1 - itn : rng[t].jlo + itn;
       const int c0 = j * ATT_BN;  // first key of the tile
       ok = __all_sync(0xffffffffu,
                       mbar_wait(bar(B_SFULL + t), itn & 1, abort_flag, p.status, ATT_ST_SOFTMAX));
@@ -1159,6 +1171,11 @@ static int attn_fwd_prepare(AttnParams& p, bool* nothing_to_do, const void* q, c
   p.win_right = window_right < 0 ? -1 : static_cast<int>(window_right > (1ll << 29) ? (1ll << 29) : window_right);
   p.is_bf16 = is_bf16;
   p.reverse_m = causal ? 1 : 0;
+  // ALiBi under a causal mask (or a window that ends at the query): the bias grows with the key
+  // index, so walking the keys forwards raises the row maximum by slope * 128 on every tile and
+  // with it comes a rescale of the whole O accumulator; walking them backwards the first tile
+  // holds the maximum and later ones never beat it by more than the lazy-rescale margin.
+  p.reverse_kv = (slopes_or_null != nullptr && (causal || window_right == 0)) ? 1 : 0;
   if (bias && Sk > 0) {
     p.bias = bias;
     p.bias_sb = bias_strides[0];
