@@ -403,10 +403,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   // the status word first.
   __shared__ int skip_launch;
 
+  // visiting order of the KV tiles: ascending, or descending from the last one
+  const int kv_step = p.reverse_kv ? -1 : 1;
+  const int kv_first = p.reverse_kv ? JHI - 1 : JLO;
   // One K or V tile into ring stage fill % STAGES (K and V tiles alternate: even fills are K).
   auto issue_fill = [&](int fill) {
     const int s = fill % ATT_STAGES;
-    const int j = p.reverse_kv ? JHI - 1 - fill / 2 : JLO + fill / 2;
+    const int j = kv_first + (fill >> 1) * kv_step;
     const bool is_k = (fill & 1) == 0;
     mbar_expect_tx(bar(B_KVFULL + s), L::TILE_BYTES);
     fills_issued[s] = fill / ATT_STAGES + 1;
@@ -563,7 +566,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       // tiles have this KV tile and the next, neither is at its first): every test below is a
       // compile-time constant and what is left is waits, MMAs, commits.
       const int n_rounds = JHI - JLO;
-      const bool rev = p.reverse_kv != 0;
+      auto run = [&](auto rev_tag) {
+      constexpr bool rev = decltype(rev_tag)::value;
       const int first0 = rev ? jhi0 - 1 : jlo0, last0 = rev ? jlo0 : jhi0 - 1;
       const int first1 = rev ? jhi1 - 1 : jlo1, last1 = rev ? jlo1 : jhi1 - 1;
       auto round = [&](int r, auto steady_tag) {
@@ -612,6 +616,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       for (; r < re && ok; ++r) round(r, std::true_type{});
 #pragma unroll 1
       for (; r < n_rounds && ok; ++r) round(r, std::false_type{});
+      };
+      if (p.reverse_kv) run(std::true_type{});
+      else run(std::false_type{});
       if (!ok) {
         // drain whatever was issued before giving up
         tc_commit(bar(B_DRAIN));
@@ -675,12 +682,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                             static_cast<long long>(row0 + rl + 8 * hr) * p.bias_sq);
     }
 
+    const int j_first = p.reverse_kv ? rng[t].jhi - 1 : rng[t].jlo;  // first KV tile visited
     float m_run[2] = {-INFINITY, -INFINITY};  // reference max (log2 domain) per row
     float l_run[2] = {0.0f, 0.0f};            // this thread's share of the row sums
     bool ok = true;
 
     for (int itn = 0; itn < n_it && ok; ++itn) {
-      const int j = p.reverse_kv ? rng[t].jhi - 1 - itn : rng[t].jlo + itn;
+      const int j = j_first + itn * kv_step;
       const int c0 = j * ATT_BN;  // first key of the tile
       ok = __all_sync(0xffffffffu,
                       mbar_wait(bar(B_SFULL + t), itn & 1, abort_flag, p.status, ATT_ST_SOFTMAX));
