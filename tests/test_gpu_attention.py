@@ -92,6 +92,24 @@ def test_causal_alibi(cuda, S):
     _check(cuda, q, k, v, causal=False, slopes=slopes)  # |i-j| on both sides
 
 
+@pytest.mark.parametrize("Sq,Sk,causal,window", [
+    (1300, 1300, True, None),          # many KV tiles, both Q tiles of a CTA, ragged tail
+    (900, 900, False, (300, 0)),       # a window that ends at the query, no causal flag
+    (1100, 1100, True, (200, 0)),      # causal and a left window: two boundary tiles per row block
+    (130, 130, True, None),            # second Q tile nearly empty
+    (256, 640, True, None),            # more keys than queries (top-left aligned mask)
+])
+def test_alibi_with_keys_visited_backwards(cuda, Sq, Sk, causal, window):
+    """ALiBi under a causal mask, or a window that ends at the query, walks a row block's KV tiles
+    from the last to the first; slopes from steep (an O rescale per tile in ascending order) to
+    flat, grouped kv heads, head dims 128 and 64."""
+    for D, H, Hk in ((128, 8, 2), (64, 4, 4)):
+        q, k, v = _qkv(2, Sq, Sk, H, Hk, D, seed=Sq + D)
+        slopes = torch.tensor([2.0 ** (-8.0 * (i + 1) / H) for i in range(H)])
+        slopes[0] = 1.5  # steeper than any standard ALiBi head
+        _check(cuda, q, k, v, causal=causal, window=window, slopes=slopes)
+
+
 @pytest.mark.parametrize("S,window", [(700, (100, 0)), (1300, (256, 0)), (600, (64, 64)),
                                       (512, (0, 0)), (900, (1024, 0)), (520, (130, 7))])
 def test_sliding_window(cuda, S, window):
