@@ -17,7 +17,9 @@
 // rescale O in TMEM only when the running row max grew by more than 2^8 (lazy rescale) and
 // run the epilogue (O / l -> global). KV tiles outside the causal / window range of a Q tile
 // are never visited; masks are applied only on boundary tiles. Query head h reads kv head
-// h / (Hq / Hk), so GQA / MQA need no tiled copies.
+// h / (Hq / Hk), so GQA / MQA need no tiled copies. With ALiBi under a causal mask the KV tiles
+// of a row block are visited from the diagonal backwards: the bias grows with the key index, so
+// in that order the first tile holds the row maximum and O is never rescaled again.
 //
 // Every wait on an mbarrier is bounded: after a fixed number of polls the kernel records a
 // code in the status word of the caller's workspace, raises a CTA-wide abort flag, drains its
@@ -41,7 +43,6 @@ constexpr int ATT_THREADS = (ATT_SM_WARPS + 2) * 32;
 constexpr uint32_t ATT_WAIT_LIMIT = 1u << 26;  // hard cap on polls per wait
 constexpr uint64_t ATT_WAIT_NS = 400ull * 1000 * 1000;  // wall-time budget of one wait
 constexpr float ATT_LAZY_RESCALE = 8.0f;       // log2 units
-constexpr int SM_COLS = ATT_BN / 2;            // score columns owned by one softmax thread
 
 enum AttnStatus : unsigned {
   ATT_ST_PRODUCER = 1u,
