@@ -526,9 +526,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         return mbar_wait(bar(b), parity, abort_flag, p.status, ATT_ST_MMA);
       };
       bool ok = true;
-      if (jhi0 > jlo0) ok = wait(B_QFULL + 0, 0);
-      if (ok && jhi1 > jlo1) ok = wait(B_QFULL + 1, 0);
       uint32_t ppar0 = 0, ppar1 = 0;  // parity of the next P hand-over per Q tile
+      // a Q tile is waited for right before its first Q K^T (the second tile lands some 700
+      // cycles after the first); the flags only exist in the general rounds
+      bool q0_ready = false, q1_ready = false;
 
       // O_t += P_t V (P from TMEM, V MN-major from ring stage `vst`); `acc` = 0 clears O first
       auto pv = [&](int t, uint32_t vst, uint32_t acc) {
@@ -590,7 +591,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             if (!STEADY && jp == last0) tc_commit(bar(B_ODONE + 0));
           }
         }
-        if (ok && (STEADY || (has_qk && jq >= jlo0 && jq < jhi0))) qk(0, kst);
+        if (ok && (STEADY || (has_qk && jq >= jlo0 && jq < jhi0))) {
+          if (!STEADY && !q0_ready) {
+            ok = wait(B_QFULL + 0, 0);
+            q0_ready = true;
+          }
+          if (ok) qk(0, kst);
+        }
         if (ok && (STEADY || (has_pv && jp >= jlo1 && jp < jhi1))) {
           ok = wait(B_PFULL + 1, ppar1);
           ppar1 ^= 1u;
@@ -599,7 +606,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             if (!STEADY && jp == last1) tc_commit(bar(B_ODONE + 1));
           }
         }
-        if (ok && (STEADY || (has_qk && jq >= jlo1 && jq < jhi1))) qk(1, kst);
+        if (ok && (STEADY || (has_qk && jq >= jlo1 && jq < jhi1))) {
+          if (!STEADY && !q1_ready) {
+            ok = wait(B_QFULL + 1, 0);
+            q1_ready = true;
+          }
+          if (ok) qk(1, kst);
+        }
         if (ok) {
           if (has_pv) tc_commit(bar(B_KVEMPTY + sv));
           if (has_qk) tc_commit(bar(B_KVEMPTY + sk));
