@@ -1,7 +1,8 @@
 // Attention forward for sm_100a: softmax(scale * Q K^T + bias) V with online softmax.
 //
-// One CTA owns 256 query rows of one (batch, head): two 128-row Q tiles that ping-pong
-// on the tensor pipe. Roles (576 threads):
+// One CTA owns two 128-row Q tiles that ping-pong on the tensor pipe: the same 128 query rows of
+// two query heads that share a kv head (GQA / MQA: both tiles then see exactly the same keys), or
+// 256 consecutive rows of one head otherwise. Roles (576 threads):
 //   warps 0-7   softmax of Q tile 0: warp w owns the 16 rows (= TMEM lanes) 32*(w%4)+16*(w/4)..,
 //               read in the 16x256b fragment shape: a quad of threads shares a row, a thread
 //               holds 2 rows x 32 columns, row maxima cost two shuffles
@@ -70,6 +71,8 @@ struct AttnParams {
   int is_bf16;
   int reverse_m;       // schedule the heaviest (last) row blocks first
   int reverse_kv;      // visit a row block's KV tiles from the last to the first
+  int pair_heads;      // the two Q tiles of a CTA: same 128 rows of two query heads that share a
+                       // kv head (1), or two consecutive 128-row blocks of one head (0)
   // dense additive mask (B, Hq, Sq, Sk) with unit key stride; batch / head strides may be 0
   const void* bias;
   long long bias_sb, bias_sh, bias_sq;  // elements
@@ -384,13 +387,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
   const int lane = threadIdx.x & 31;
 
   const int mblk = p.reverse_m ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
-  const int h = blockIdx.y;
   const int b = blockIdx.z;
-  const int m0 = mblk * (ATT_NQ * ATT_BM);
+  // Q tile t of this CTA: rows m0 + t * t_rows .. + 127 of query head h + t * t_head. Paired heads
+  // see the same keys, so both tiles are active in every round; paired row blocks differ by one
+  // KV tile at either end of their ranges, where one tile then works alone.
+  const int t_rows = p.pair_heads ? 0 : ATT_BM;
+  const int t_head = p.pair_heads ? 1 : 0;
+  const int h = p.pair_heads ? 2 * blockIdx.y : blockIdx.y;
+  const int m0 = mblk * (p.pair_heads ? ATT_BM : ATT_NQ * ATT_BM);
 
   TileRange rng[ATT_NQ];
 #pragma unroll
-  for (int t = 0; t < ATT_NQ; ++t) rng[t] = tile_range(p, m0 + t * ATT_BM);
+  for (int t = 0; t < ATT_NQ; ++t) rng[t] = tile_range(p, m0 + t * t_rows);
   int JLO = 1 << 30, JHI = 0;
 #pragma unroll
   for (int t = 0; t < ATT_NQ; ++t)
@@ -456,7 +464,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 #pragma unroll
           for (int c = 0; c < L::CHUNKS; ++c)
             tma_load_4d(sbase + L::Q_OFF + t * L::TILE_BYTES + c * L::CHUNK_BYTES, &p.tm_q,
-                        bar(B_QFULL + t), c * 64, m0 + t * ATT_BM, h, b);
+                        bar(B_QFULL + t), c * 64, m0 + t * t_rows, h + t * t_head, b);
         }
       }
       // the ring is empty: its first round of fills waits for nobody
@@ -656,7 +664,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     const int sub = (warp >> 2) & 1;                        // which 16 lanes of the quarter
     const int q4 = lane & 3;                                // position in the quad
     const int rl = wq * 32 + sub * 16 + (lane >> 2);        // first row (second is rl + 8)
-    const int row0 = m0 + t * ATT_BM;                       // first row of the Q tile
+    const int row0 = m0 + t * t_rows;                       // first row of the Q tile
+    const int hq = h + t * t_head;                          // query head of the Q tile
     const int row1 = min(p.Sq, row0 + ATT_BM) - 1;
     const uint32_t lane16 = static_cast<uint32_t>(wq * 32 + sub * 16) << 16;
     const uint32_t s_addr = tmem_base + lane16 + t * ATT_BN;
@@ -680,7 +689,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     if (p.win_left >= 0) lo_max = max(0, row1 - p.win_left);
 
     const float sl2 = p.scale_log2;
-    const float slope2 = p.slopes ? p.slopes[h] * 1.4426950408889634f : 0.0f;
+    const float slope2 = p.slopes ? p.slopes[hq] * 1.4426950408889634f : 0.0f;
     const bool has_alibi = p.slopes != nullptr;
     const bool has_bias = BIAS && p.bias_kind != 0;
     const bool has_drop = BIAS && p.drop_thr != 0u;
@@ -692,7 +701,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       for (int hr = 0; hr < 2; ++hr)
         if (row0 + rl + 8 * hr < p.Sq)
           brow[hr] = reinterpret_cast<const uint8_t*>(p.bias) +
-                     esz * (b * p.bias_sb + h * p.bias_sh +
+                     esz * (b * p.bias_sb + hq * p.bias_sh +
                             static_cast<long long>(row0 + rl + 8 * hr) * p.bias_sq);
     }
 
@@ -867,7 +876,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 rnd[hr] = philox4x32_10(
                     make_uint4(static_cast<uint32_t>((c0 + 8 * g) >> 4),
                                static_cast<uint32_t>(row_g[hr]),
-                               static_cast<uint32_t>(b * p.Hq + h), p.drop_offset),
+                               static_cast<uint32_t>(b * p.Hq + hq), p.drop_offset),
                     p.seed_lo, p.seed_hi);
               // keys 8g + 2*q4 + {0, 1} of the tile = bytes 8(g&1) + 2*q4 + {0, 1} of the block
               const int lc = 8 * (g & 1) + 2 * q4;
@@ -958,7 +967,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                               t * ATT_BN + sub * OC;
       uint8_t* orow = reinterpret_cast<uint8_t*>(p.out) +
                       2ll * (b * p.o_stride_b + static_cast<long long>(row) * p.o_stride_s +
-                             h * p.o_stride_h + sub * OC);
+                             hq * p.o_stride_h + sub * OC);
 #pragma unroll
       for (int cc = 0; cc < OC; cc += 32) {
         uint32_t orr[32];
@@ -988,7 +997,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         const float lse = (n_it > 0 && l_row > 0.0f)
                               ? (m_row + log2f(l_row)) * 0.6931471805599453f
                               : -INFINITY;
-        p.lse[b * p.lse_stride_b + h * p.lse_stride_h + row] = lse;
+        p.lse[b * p.lse_stride_b + hq * p.lse_stride_h + row] = lse;
       }
     }
   }
@@ -1092,8 +1101,9 @@ static int launch_attn_bias(const AttnParams& p, cudaStream_t stream) {
       return TRX_ERR_CUDA;
     if (cacheable) configured[dev].store(true, std::memory_order_release);
   }
-  const int mblocks = (p.Sq + ATT_NQ * ATT_BM - 1) / (ATT_NQ * ATT_BM);
-  dim3 grid(mblocks, p.Hq, p.B);
+  const int rows_per_cta = p.pair_heads ? ATT_BM : ATT_NQ * ATT_BM;
+  const int mblocks = (p.Sq + rows_per_cta - 1) / rows_per_cta;
+  dim3 grid(mblocks, p.pair_heads ? p.Hq / 2 : p.Hq, p.B);
   attn_fwd_kernel<D, BF16, BIAS><<<grid, ATT_THREADS, AttnSmem<D>::DYN_BYTES, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? TRX_OK : TRX_ERR_CUDA;
 }
@@ -1198,6 +1208,8 @@ static int attn_fwd_prepare(AttnParams& p, bool* nothing_to_do, const void* q, c
   // with it comes a rescale of the whole O accumulator; walking them backwards the first tile
   // holds the maximum and later ones never beat it by more than the lazy-rescale margin.
   p.reverse_kv = (slopes_or_null != nullptr && (causal || window_right == 0)) ? 1 : 0;
+  // two query heads per CTA when each pair (2i, 2i + 1) reads one kv head in K and in V
+  p.pair_heads = (Hq % 2 == 0 && p.k_hdiv % 2 == 0 && p.v_hdiv % 2 == 0) ? 1 : 0;
   if (bias && Sk > 0) {
     p.bias = bias;
     p.bias_sb = bias_strides[0];
